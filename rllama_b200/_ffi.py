@@ -1,0 +1,94 @@
+"""ctypes view of the C ABI declared in ``include/rllama_b200.h``.
+
+The shared library is built in-tree by ``rllama_b200.build``. There is no CPU fallback:
+importing this module without the built library raises, and every entry point fails with
+an ``RllamaError`` when no sm_100 device is usable.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librllama_b200.so")
+
+F32, F16 = 0, 1
+
+# every symbol include/rllama_b200.h declares
+EXPORTS = [
+    "rlb_last_error", "rlb_device_count",
+    "rlb_ctx_create", "rlb_ctx_destroy", "rlb_ctx_flush", "rlb_ctx_kernel_launches",
+    "rlb_tensor_upload", "rlb_tensor_zeros", "rlb_tensor_wait", "rlb_tensor_download", "rlb_event_wait", "rlb_tensor_free",
+    "rlb_copy_inplace", "rlb_transpose_from", "rlb_hadamard_product_inplace", "rlb_silu_inplace",
+    "rlb_matrix_mul_inplace_transposed",
+    "rlb_model_create", "rlb_model_set_tensor", "rlb_model_finalize", "rlb_model_free",
+    "rlb_tp_nccl_unique_id", "rlb_tp_nccl_init", "rlb_tp_peer_export", "rlb_tp_peer_import", "rlb_tp_set_mode",
+    "rlb_caches_create", "rlb_caches_true_clone", "rlb_caches_shift_left", "rlb_caches_free", "rlb_caches_read",
+    "rlb_forward", "rlb_forward_greedy", "rlb_decode_greedy",
+    "rlb_model_set_option", "rlb_model_get_stat",
+]
+
+
+class RllamaError(RuntimeError):
+    """A non-zero status from the library (the reference panics or returns Err here)."""
+
+    def __init__(self, status, message):
+        super().__init__("rllama_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+class ModelParams(ctypes.Structure):
+    _fields_ = [
+        ("dim", ctypes.c_int32), ("n_layers", ctypes.c_int32), ("n_heads", ctypes.c_int32),
+        ("ffn_dim", ctypes.c_int32), ("vocab_size", ctypes.c_int32), ("max_seq_len", ctypes.c_int32),
+        ("norm_eps", ctypes.c_float), ("force_f16", ctypes.c_int32),
+        ("tp_rank", ctypes.c_int32), ("tp_size", ctypes.c_int32),
+    ]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "librllama_b200.so is not built (run `python -m rllama_b200.build`); there is no CPU fallback")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, ci, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int32, ctypes.c_int64
+    P = ctypes.POINTER
+    L.rlb_last_error.restype = ctypes.c_char_p
+    L.rlb_last_error.argtypes = []
+    sig = {
+        "rlb_device_count": [P(ci)],
+        "rlb_ctx_create": [ci, ci, P(vp)], "rlb_ctx_destroy": [vp], "rlb_ctx_flush": [vp],
+        "rlb_ctx_kernel_launches": [vp, P(ctypes.c_uint64)],
+        "rlb_tensor_upload": [vp, vp, i64, i64, i64, ci, P(vp)],
+        "rlb_tensor_zeros": [vp, i64, i64, i64, ci, P(vp)],
+        "rlb_tensor_wait": [vp], "rlb_tensor_download": [vp, vp, P(vp)], "rlb_event_wait": [vp], "rlb_tensor_free": [vp],
+        "rlb_copy_inplace": [vp, vp], "rlb_transpose_from": [vp, vp], "rlb_hadamard_product_inplace": [vp, vp],
+        "rlb_silu_inplace": [vp], "rlb_matrix_mul_inplace_transposed": [vp, vp, vp],
+        "rlb_model_create": [vp, P(ModelParams), P(vp)],
+        "rlb_model_set_tensor": [vp, ci, i32, vp, i64, i64, i64, ci],
+        "rlb_model_finalize": [vp], "rlb_model_free": [vp],
+        "rlb_tp_nccl_unique_id": [vp], "rlb_tp_nccl_init": [vp, vp],
+        "rlb_tp_peer_export": [vp, vp], "rlb_tp_peer_import": [vp, vp, i32], "rlb_tp_set_mode": [vp, i32],
+        "rlb_caches_create": [vp, P(vp)], "rlb_caches_true_clone": [vp, P(vp)], "rlb_caches_shift_left": [vp, i32],
+        "rlb_caches_free": [vp], "rlb_caches_read": [vp, i32, i32, i32, i32, vp],
+        "rlb_forward": [vp, vp, vp, i32, i32, vp],
+        "rlb_forward_greedy": [vp, vp, vp, i32, i32, P(i32)],
+        "rlb_decode_greedy": [vp, vp, i32, i32, i32, vp, P(ctypes.c_float)],
+        "rlb_model_set_option": [vp, ctypes.c_char_p, i64],
+        "rlb_model_get_stat": [vp, ctypes.c_char_p, P(ctypes.c_double)],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name)
+        fn.restype = ci
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+def check(status):
+    if status != 0:
+        raise RllamaError(status, lib().rlb_last_error().decode("utf-8", "replace"))

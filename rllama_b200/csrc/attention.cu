@@ -1,0 +1,274 @@
+// Attention over the KV cache: the per-head part of Attention::forward
+// (src/transformer.rs:727-781): scores = q * K / sqrt(head_dim), causal mask for multi-token
+// calls (Tensor::full_triu, src/tensor.rs:496-508), softmax (src/tensor.rs:479-494),
+// out = P * V. Everything is f32 arithmetic on cache values widened from their storage
+// dtype, as in the reference (:762-766).
+//
+// The reference's softmax does not subtract the row maximum; the kernels here do (and the
+// split-T decode kernel combines partial results with the usual rescaling). That is the same
+// function of the inputs, evaluated without overflow; results differ by f32 rounding only.
+//
+// Cache layout in HBM: per layer, K and V are [head][position][head_dim] (position-major,
+// one 128/256-byte row per position) instead of the reference's head_dim x max_seq_len per
+// head, so that one position's vector is a single coalesced read.
+#include "internal.h"
+
+#include <cfloat>
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <typename T> struct CVec;
+template <> struct CVec<__half> { static constexpr int N = 8; };
+template <> struct CVec<float> { static constexpr int N = 4; };
+
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& v, float* f);
+template <> __device__ __forceinline__ void unpack16<__half>(const uint4& v, float* f) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+
+template <typename T> __device__ __forceinline__ T cast_out(float v);
+template <> __device__ __forceinline__ __half cast_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float cast_out<float>(float v) { return v; }
+
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; w++) t = fmaxf(t, red[w]);
+    __syncthreads();
+    return t;
+}
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) t += red[w];
+    __syncthreads();
+    return t;
+}
+
+// One query row against positions [t0, t1) of one head. Shared memory: q[hd], sc[t1-t0],
+// acc[kThreads/tpp][hd]. Produces the unnormalised output o[hd] (in shared `o_out`), the
+// running maximum m and the sum l = sum exp(s - m).
+template <typename CT>
+__device__ void attend_range(const float* __restrict__ q_sh, const CT* __restrict__ kbase, const CT* __restrict__ vbase,
+                             int hd, int t0, int t1, float scale, float* sc, float* accbuf, float* red, float* o_out,
+                             float& m_out, float& l_out) {
+    constexpr int VEC = CVec<CT>::N;
+    const int tid = threadIdx.x;
+    const int n = t1 - t0;
+    // ---- scores: a group of (hd / VEC) threads... 8 lanes per position, each lane hd/8 dims ----
+    {
+        const int lpp = 8;                    // lanes per position
+        const int dpl = hd / lpp;             // dims per lane (multiple of VEC)
+        const int sub = tid & (lpp - 1);
+        const int slot = tid / lpp;           // position slot within an iteration
+        const int ppi = kThreads / lpp;       // positions per iteration
+        for (int i = slot; i < ((n + ppi - 1) / ppi) * ppi; i += ppi) {
+            float dot = 0.f;
+            if (i < n) {
+                const CT* kp = kbase + (int64_t)(t0 + i) * hd + sub * dpl;
+                const float* qp = q_sh + sub * dpl;
+                for (int d = 0; d < dpl; d += VEC) {
+                    float kf[VEC];
+                    unpack16<CT>(*reinterpret_cast<const uint4*>(kp + d), kf);
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) dot = fmaf(qp[d + e], kf[e], dot);
+                }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (sub == 0 && i < n) sc[i] = dot * scale;
+        }
+    }
+    __syncthreads();
+    // ---- softmax pieces ----
+    float m = -FLT_MAX;
+    for (int i = tid; i < n; i += kThreads) m = fmaxf(m, sc[i]);
+    m = block_reduce_max(m, red);
+    float l = 0.f;
+    for (int i = tid; i < n; i += kThreads) {
+        const float p = expf(sc[i] - m);
+        sc[i] = p;
+        l += p;
+    }
+    l = block_reduce_sum(l, red);
+    // ---- o = sum_t p[t] * V[t] : (hd / VEC) threads per position ----
+    {
+        const int tpp = hd / VEC;
+        const int sub = tid % tpp;
+        const int slot = tid / tpp;
+        const int ppi = kThreads / tpp;
+        float acc[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; e++) acc[e] = 0.f;
+        if (slot < ppi) {
+            for (int i = slot; i < n; i += ppi) {
+                float vf[VEC];
+                unpack16<CT>(*reinterpret_cast<const uint4*>(vbase + (int64_t)(t0 + i) * hd + sub * VEC), vf);
+                const float p = sc[i];
+#pragma unroll
+                for (int e = 0; e < VEC; e++) acc[e] = fmaf(p, vf[e], acc[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; e++) accbuf[slot * hd + sub * VEC + e] = acc[e];
+        }
+        __syncthreads();
+        for (int c = tid; c < hd; c += kThreads) {
+            float s = 0.f;
+            for (int j = 0; j < ppi; j++) s += accbuf[j * hd + c];
+            o_out[c] = s;
+        }
+        __syncthreads();
+    }
+    m_out = m;
+    l_out = l;
+}
+
+// grid (heads, n_split). Scratch record per (head, split): o[hd], m, l.
+template <typename CT>
+__global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnDecodeArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[kWarps];
+    __shared__ unsigned int ticket_sh;
+    const int hd = a.hd, head = blockIdx.x, split = blockIdx.y, ns = a.n_split;
+    const int T = *a.pos_ptr + 1;
+    int chunk = (T + ns - 1) / ns;
+    chunk = (chunk + 31) & ~31;
+    const int t0 = min(T, split * chunk), t1 = min(T, t0 + chunk);
+    float* q_sh = sm;                 // hd
+    float* o_sh = q_sh + hd;          // hd
+    float* accbuf = o_sh + hd;        // (kThreads / (hd / VEC)) * hd  <= kThreads * VEC
+    float* sc = accbuf + kThreads * CVec<CT>::N;  // chunk (sized for max_seq / 1)
+    for (int c = threadIdx.x; c < hd; c += kThreads) q_sh[c] = a.q[head * hd + c];
+    __syncthreads();
+    const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * hd;
+    const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * hd;
+    const float scale = 1.0f / sqrtf((float)hd);  // src/transformer.rs:770
+    float m = -FLT_MAX, l = 0.f;
+    if (t1 > t0) {
+        attend_range<CT>(q_sh, kbase, vbase, hd, t0, t1, scale, sc, accbuf, red, o_sh, m, l);
+    } else {
+        for (int c = threadIdx.x; c < hd; c += kThreads) o_sh[c] = 0.f;
+        __syncthreads();
+    }
+    CT* out = reinterpret_cast<CT*>(a.out) + head * hd;
+    if (ns == 1) {
+        for (int c = threadIdx.x; c < hd; c += kThreads) out[c] = cast_out<CT>(o_sh[c] / l);
+        return;
+    }
+    float* rec = a.scratch + ((int64_t)head * ns + split) * (hd + 2);
+    for (int c = threadIdx.x; c < hd; c += kThreads) rec[c] = o_sh[c];
+    if (threadIdx.x == 0) { rec[hd] = m; rec[hd + 1] = l; }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_sh = atomicAdd(a.counters + head, 1u);
+    __syncthreads();
+    if (ticket_sh != (unsigned)(ns - 1)) return;
+    // last CTA of this head: combine the partial results
+    __threadfence();
+    const float* recs = a.scratch + (int64_t)head * ns * (hd + 2);
+    float M = -FLT_MAX;
+    for (int s = 0; s < ns; s++) M = fmaxf(M, __ldcg(recs + s * (hd + 2) + hd));
+    float L = 0.f;
+    for (int s = 0; s < ns; s++) L += __ldcg(recs + s * (hd + 2) + hd + 1) * expf(__ldcg(recs + s * (hd + 2) + hd) - M);
+    for (int c = threadIdx.x; c < hd; c += kThreads) {
+        float o = 0.f;
+        for (int s = 0; s < ns; s++) o += __ldcg(recs + s * (hd + 2) + c) * expf(__ldcg(recs + s * (hd + 2) + hd) - M);
+        out[c] = cast_out<CT>(o / L);
+    }
+    if (threadIdx.x == 0) a.counters[head] = 0;  // ready for the next launch
+}
+
+// Prefill: grid (heads, n); one CTA per (head, query row i) attends to positions 0..start_pos+i.
+template <typename CT>
+__global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefillArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[kWarps];
+    const int hd = a.hd, head = blockIdx.x, i = blockIdx.y;
+    const int T = a.start_pos + i + 1;  // mask: col >= row + start_pos + 1 is -inf
+    float* q_sh = sm;
+    float* o_sh = q_sh + hd;
+    float* accbuf = o_sh + hd;
+    float* sc = accbuf + kThreads * CVec<CT>::N;
+    for (int c = threadIdx.x; c < hd; c += kThreads) q_sh[c] = a.q[(int64_t)i * a.heads * hd + head * hd + c];
+    __syncthreads();
+    const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * hd;
+    const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * hd;
+    const float scale = 1.0f / sqrtf((float)hd);
+    float m, l;
+    attend_range<CT>(q_sh, kbase, vbase, hd, 0, T, scale, sc, accbuf, red, o_sh, m, l);
+    CT* out = reinterpret_cast<CT*>(a.out) + (int64_t)i * a.heads * hd + head * hd;
+    for (int c = threadIdx.x; c < hd; c += kThreads) out[c] = cast_out<CT>(o_sh[c] / l);
+}
+
+size_t attn_smem_bytes(int hd, int vec, int max_positions) {
+    return sizeof(float) * ((size_t)2 * hd + (size_t)kThreads * vec + (size_t)max_positions);
+}
+
+}  // namespace
+
+size_t attn_decode_scratch_floats(int heads, int hd, int n_split) { return (size_t)heads * n_split * (hd + 2); }
+
+int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a) {
+    const int vec = cache_dtype == RLB_F16 ? 8 : 4;
+    if (a.hd % 8 != 0 || (a.hd / 8) % vec != 0 || a.hd / vec > kThreads)
+        return rlb_fail(RLB_ERR_INVALID, "attention: head_dim %d is not supported", a.hd);
+    int chunk = (a.max_seq + a.n_split - 1) / a.n_split;
+    chunk = (chunk + 31) & ~31;
+    const size_t smem = attn_smem_bytes(a.hd, vec, chunk);
+    if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "attention: %d positions per CTA do not fit in shared memory", chunk);
+    dim3 grid(a.heads, a.n_split);
+    if (cache_dtype == RLB_F16) {
+        static bool set = false;
+        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        attn_decode_kernel<__half><<<grid, kThreads, smem, ctx->stream>>>(a);
+    } else {
+        static bool set = false;
+        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        attn_decode_kernel<float><<<grid, kThreads, smem, ctx->stream>>>(a);
+    }
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillArgs& a) {
+    const int vec = cache_dtype == RLB_F16 ? 8 : 4;
+    if (a.hd % 8 != 0 || (a.hd / 8) % vec != 0 || a.hd / vec > kThreads)
+        return rlb_fail(RLB_ERR_INVALID, "attention: head_dim %d is not supported", a.hd);
+    const size_t smem = attn_smem_bytes(a.hd, vec, a.start_pos + a.n);
+    if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "attention: %d positions do not fit in shared memory", a.start_pos + a.n);
+    dim3 grid(a.heads, a.n);
+    if (cache_dtype == RLB_F16) {
+        static bool set = false;
+        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        attn_prefill_kernel<__half><<<grid, kThreads, smem, ctx->stream>>>(a);
+    } else {
+        static bool set = false;
+        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        attn_prefill_kernel<float><<<grid, kThreads, smem, ctx->stream>>>(a);
+    }
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}

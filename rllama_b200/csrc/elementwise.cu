@@ -1,0 +1,313 @@
+// Row-wise and element-wise kernels: the multi-token (prefill) forms of RMSNorm, RoPE +
+// cache append, SiLU gate and residual add, the arg-max used for greedy decoding, and the
+// tier-1 element-wise ops that replace rllama's OpenCL kernels silu_f16, hadamard_product_f16
+// and transpose_f16 (src/tensor_opencl_support.rs:668-715).
+#include "internal.h"
+
+#include <cfloat>
+
+namespace {
+
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+
+template <typename T> __device__ __forceinline__ T cast_to(float v);
+template <> __device__ __forceinline__ __half cast_to<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float cast_to<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+
+// Embedding::get_embedding + Tensor::concat (src/embedding.rs:50-52, src/tensor.rs:736-766)
+__global__ void embed_kernel(const float* __restrict__ table, const int32_t* __restrict__ tokens, int dim, float* __restrict__ x) {
+    const int row = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(table + (int64_t)tokens[row] * dim);
+    float4* dst = reinterpret_cast<float4*>(x + (int64_t)row * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// RMSNorm::forward (src/transformer.rs:476-480), one CTA per row.
+template <typename OT>
+__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, int dim, const float* __restrict__ gain, float eps, OT* __restrict__ out) {
+    __shared__ float red[32];
+    const float* xr = x + (int64_t)blockIdx.x * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) tot += red[w];
+    const float scale = 1.0f / sqrtf(tot / (float)dim + eps);
+    OT* o = out + (int64_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = cast_to<OT>(__fmul_rn(__fmul_rn(xr[i], scale), gain[i]));
+}
+
+// apply_rotary_emb (src/transformer.rs:823-856) + the cache write loop (:751-761).
+template <typename CT>
+__global__ void rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int start_pos,
+                                   int heads, int hd, int max_seq, const float* __restrict__ rope, CT* __restrict__ kcache,
+                                   CT* __restrict__ vcache) {
+    const int i = blockIdx.x, pos = start_pos + i, nq = heads * hd;
+    for (int p = threadIdx.x; p < nq / 2; p += blockDim.x) {
+        const int head = (2 * p) / hd, c = 2 * p - head * hd;
+        const float fr = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2], fi = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2 + 1];
+        const int64_t idx = (int64_t)i * nq + 2 * p;
+        const float qr = q[idx], qi = q[idx + 1], kr = k[idx], ki = k[idx + 1];
+        q[idx] = __fsub_rn(__fmul_rn(qr, fr), __fmul_rn(qi, fi));
+        q[idx + 1] = __fadd_rn(__fmul_rn(qr, fi), __fmul_rn(qi, fr));
+        const int64_t cidx = ((int64_t)head * max_seq + pos) * hd + c;
+        kcache[cidx] = cast_to<CT>(__fsub_rn(__fmul_rn(kr, fr), __fmul_rn(ki, fi)));
+        kcache[cidx + 1] = cast_to<CT>(__fadd_rn(__fmul_rn(kr, fi), __fmul_rn(ki, fr)));
+        vcache[cidx] = cast_to<CT>(v[idx]);
+        vcache[cidx + 1] = cast_to<CT>(v[idx + 1]);
+    }
+}
+
+// silu_cpu + hadamard_product_cpu (src/tensor.rs:822-832, :722-734) and the cast before w2.
+template <typename OT>
+__global__ void swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t count, OT* __restrict__ out) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = a1[i];
+        const float s = v / (1.0f + expf(-v));
+        out[i] = cast_to<OT>(__fmul_rn(s, a3[i]));
+    }
+}
+
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t count, int do_round) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] += do_round ? round_f16(y[i]) : y[i];
+}
+
+// Greedy choice = TokenSampler with top_k 1 (src/token_sampler.rs:20-28, :127-147): the
+// largest logit; among equal maxima the lowest id (the reference's unstable sort leaves ties
+// unspecified). NaNs sort last, as in the reference's comparator.
+__device__ __forceinline__ void argmax_block(const float* __restrict__ logits, int n, float& best_v, int& best_i) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    bv = sv[0]; bi = si[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+        if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    if (bi == 0x7fffffff) bi = 0;
+    best_v = bv; best_i = bi;
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int n, int32_t* __restrict__ out_tok) {
+    float bv; int bi;
+    argmax_block(logits, n, bv, bi);
+    if (threadIdx.x == 0) *out_tok = bi;
+}
+
+__global__ void argmax_advance_kernel(const float* __restrict__ logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
+                                      int32_t* tokens_out, int32_t cap) {
+    float bv; int bi;
+    argmax_block(logits, n, bv, bi);
+    if (threadIdx.x == 0) {
+        *tok = bi;
+        *pos = *pos + 1;
+        const int s = *step;
+        if (s < cap) tokens_out[s] = bi;
+        *step = s + 1;
+    }
+}
+
+template <typename ST, typename DT>
+__global__ void convert_kernel(const ST* __restrict__ src, int64_t src_ld, DT* __restrict__ dst, int64_t dst_ld, int64_t rows, int64_t cols) {
+    const int64_t total = rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i - r * cols;
+        dst[r * dst_ld + c] = cast_to<DT>(to_f32<ST>(src[r * src_ld + c]));
+    }
+}
+
+// silu_f16 (src/tensor_opencl_support.rs:668-680): x * 1/(1+exp(-x)) in f32, in place.
+template <typename T>
+__global__ void silu_kernel(T* t, int64_t rows, int64_t cols, int64_t cap) {
+    const int64_t total = rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i - r * cols;
+        const float v = to_f32<T>(t[r * cap + c]);
+        t[r * cap + c] = cast_to<T>(v * (1.0f / (1.0f + expf(-v))));
+    }
+}
+
+// hadamard_product_f16 (src/tensor_opencl_support.rs:683-697)
+template <typename T>
+__global__ void hadamard_kernel(T* dst, const T* __restrict__ other, int64_t rows, int64_t cols, int64_t dcap, int64_t ocap) {
+    const int64_t total = rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / cols, c = i - r * cols;
+        dst[r * dcap + c] = cast_to<T>(to_f32<T>(dst[r * dcap + c]) * to_f32<T>(other[r * ocap + c]));
+    }
+}
+
+// transpose_f16 (src/tensor_opencl_support.rs:700-715), tiled through shared memory.
+template <typename T>
+__global__ void transpose_kernel(T* __restrict__ dst, const T* __restrict__ src, int64_t drows, int64_t dcols, int64_t dcap, int64_t scap) {
+    __shared__ T tile[32][33];
+    const int64_t sr0 = (int64_t)blockIdx.x * 32, sc0 = (int64_t)blockIdx.y * 32;  // src rows = dst cols
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int64_t sr = sr0 + j, sc = sc0 + threadIdx.x;
+        if (sr < dcols && sc < drows) tile[j][threadIdx.x] = src[sr * scap + sc];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        const int64_t dr = sc0 + j, dc = sr0 + threadIdx.x;
+        if (dr < drows && dc < dcols) dst[dr * dcap + dc] = tile[threadIdx.x][j];
+    }
+}
+
+// AttentionCache::shift_left (src/transformer.rs:180-197) on the position-major layout: every
+// position row moves `shifts` rows towards 0. One CTA per head; rows are moved in ascending
+// order with a barrier between batches so that a row is read before it is overwritten.
+template <typename T>
+__global__ void shift_left_kernel(T* cache, int max_seq, int hd, int shifts) {
+    T* base = cache + (int64_t)blockIdx.x * max_seq * hd;
+    // the reference repeats a one-step shift `shifts` times; the last `shifts` rows keep the
+    // value of the final row
+    const int64_t n_move = (int64_t)(max_seq - shifts) * hd;
+    const int64_t off = (int64_t)shifts * hd;
+    for (int64_t b = 0; b < n_move; b += blockDim.x) {
+        const int64_t i = b + threadIdx.x;
+        T v = T();
+        if (i < n_move) v = base[i + off];
+        __syncthreads();
+        if (i < n_move) base[i] = v;
+        __syncthreads();
+    }
+    // rows max_seq - shifts .. max_seq - 2 take the last row's value; the last row is unchanged
+    for (int64_t i = threadIdx.x; i < (int64_t)(shifts - 1) * hd; i += blockDim.x) {
+        const int64_t r = max_seq - shifts + i / hd, c = i % hd;
+        base[r * hd + c] = base[(int64_t)(max_seq - 1) * hd + c];
+    }
+}
+
+inline int grid_for(int64_t n, int block = 256, int cap = 148 * 8) {
+    int64_t g = (n + block - 1) / block;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace
+
+int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, int n, int dim, float* x) {
+    embed_kernel<<<n, 256, 0, ctx->stream>>>(table, tokens_dev, dim, x);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype, void* out) {
+    if (out_dtype == RLB_F16) rmsnorm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, dim, gain, eps, (__half*)out);
+    else rmsnorm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, dim, gain, eps, (float*)out);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int n, int start_pos, int heads, int hd, int max_seq,
+                       const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache) {
+    if (cache_dtype == RLB_F16)
+        rope_append_kernel<__half><<<n, 256, 0, ctx->stream>>>(q, k, v, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
+    else
+        rope_append_kernel<float><<<n, 256, 0, ctx->stream>>>(q, k, v, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t count, rlb_dtype out_dtype, void* out) {
+    if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, count, (__half*)out);
+    else swiglu_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, count, (float*)out);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int round_f16_flag) {
+    add_rows_kernel<<<grid_for(count), 256, 0, ctx->stream>>>(x, y, count, round_f16_flag);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok) {
+    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, out_tok);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step, int32_t* tokens_out,
+                          int32_t tokens_cap) {
+    argmax_advance_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, tok, pos, step, tokens_out, tokens_cap);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_convert(rlb_ctx* ctx, const void* src, rlb_dtype sdt, int64_t src_ld, void* dst, rlb_dtype ddt, int64_t dst_ld, int64_t rows,
+                   int64_t cols) {
+    const int g = grid_for(rows * cols);
+    if (sdt == RLB_F16 && ddt == RLB_F16) convert_kernel<__half, __half><<<g, 256, 0, ctx->stream>>>((const __half*)src, src_ld, (__half*)dst, dst_ld, rows, cols);
+    else if (sdt == RLB_F16 && ddt == RLB_F32) convert_kernel<__half, float><<<g, 256, 0, ctx->stream>>>((const __half*)src, src_ld, (float*)dst, dst_ld, rows, cols);
+    else if (sdt == RLB_F32 && ddt == RLB_F16) convert_kernel<float, __half><<<g, 256, 0, ctx->stream>>>((const float*)src, src_ld, (__half*)dst, dst_ld, rows, cols);
+    else convert_kernel<float, float><<<g, 256, 0, ctx->stream>>>((const float*)src, src_ld, (float*)dst, dst_ld, rows, cols);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_silu(rlb_ctx* ctx, void* t, rlb_dtype dtype, int64_t rows, int64_t cols, int64_t cap) {
+    const int g = grid_for(rows * cols);
+    if (dtype == RLB_F16) silu_kernel<__half><<<g, 256, 0, ctx->stream>>>((__half*)t, rows, cols, cap);
+    else silu_kernel<float><<<g, 256, 0, ctx->stream>>>((float*)t, rows, cols, cap);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_hadamard(rlb_ctx* ctx, void* dst, const void* other, rlb_dtype dtype, int64_t rows, int64_t cols, int64_t dcap, int64_t ocap) {
+    const int g = grid_for(rows * cols);
+    if (dtype == RLB_F16) hadamard_kernel<__half><<<g, 256, 0, ctx->stream>>>((__half*)dst, (const __half*)other, rows, cols, dcap, ocap);
+    else hadamard_kernel<float><<<g, 256, 0, ctx->stream>>>((float*)dst, (const float*)other, rows, cols, dcap, ocap);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_transpose(rlb_ctx* ctx, void* dst, const void* src, rlb_dtype dtype, int64_t drows, int64_t dcols, int64_t dcap, int64_t scap) {
+    dim3 grid((unsigned)((dcols + 31) / 32), (unsigned)((drows + 31) / 32)), block(32, 8);
+    if (grid.y > 65535) return rlb_fail(RLB_ERR_LIMIT, "transpose: more than 2097120 rows");
+    if (dtype == RLB_F16) transpose_kernel<__half><<<grid, block, 0, ctx->stream>>>((__half*)dst, (const __half*)src, drows, dcols, dcap, scap);
+    else transpose_kernel<float><<<grid, block, 0, ctx->stream>>>((float*)dst, (const float*)src, drows, dcols, dcap, scap);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+int launch_cache_shift_left(rlb_ctx* ctx, void* cache, rlb_dtype dtype, int64_t heads, int max_seq, int hd, int shifts) {
+    if (shifts <= 0) return RLB_OK;
+    if (shifts >= max_seq) shifts = max_seq - 1;
+    if (shifts <= 0) return RLB_OK;
+    if (dtype == RLB_F16) shift_left_kernel<__half><<<(unsigned)heads, 1024, 0, ctx->stream>>>((__half*)cache, max_seq, hd, shifts);
+    else shift_left_kernel<float><<<(unsigned)heads, 1024, 0, ctx->stream>>>((float*)cache, max_seq, hd, shifts);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}

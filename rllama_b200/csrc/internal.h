@@ -1,0 +1,189 @@
+// Internal declarations shared by the translation units of librllama_b200.so.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/rllama_b200.h"
+
+// ---------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------
+int rlb_fail(int code, const char* fmt, ...);  // records the thread's message, returns code
+
+#define RLB_CUDA(expr)                                                                         \
+    do {                                                                                       \
+        cudaError_t _e = (expr);                                                               \
+        if (_e != cudaSuccess)                                                                 \
+            return rlb_fail(_e == cudaErrorMemoryAllocation ? RLB_ERR_OOM : RLB_ERR_CUDA,      \
+                            "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__,  \
+                            __LINE__);                                                         \
+    } while (0)
+
+#define RLB_TRY(expr)            \
+    do {                         \
+        int _s = (expr);         \
+        if (_s != RLB_OK) return _s; \
+    } while (0)
+
+// ---------------------------------------------------------------------------------------
+// handles
+// ---------------------------------------------------------------------------------------
+struct rlb_ctx {
+    int device = 0;
+    int sm_count = 0;
+    bool verbose = false;
+    cudaStream_t stream = nullptr;
+    std::recursive_mutex mu;
+    uint64_t launches = 0;  // kernels launched by this library on this context
+};
+
+struct rlb_tensor {
+    rlb_ctx* ctx = nullptr;
+    void* d = nullptr;
+    int64_t rows = 0, cols = 0, cap = 0;
+    rlb_dtype dtype = RLB_F32;
+    cudaEvent_t ready = nullptr;  // last operation queued on this tensor
+    size_t bytes() const { return (size_t)rows * cap * (dtype == RLB_F16 ? 2 : 4); }
+};
+
+struct rlb_event {
+    rlb_ctx* ctx = nullptr;
+    cudaEvent_t ev = nullptr;
+};
+
+static inline size_t dtype_size(rlb_dtype t) { return t == RLB_F16 ? 2 : 4; }
+
+// ---------------------------------------------------------------------------------------
+// decode GEMV family (gemv.cu)
+// ---------------------------------------------------------------------------------------
+enum GemvPrologue {
+    PRO_COPY = 0,  // activation already in the weight dtype: act[k] = vec_in[k]
+    PRO_NORM = 1,  // act = cast(rmsnorm(x_in + round(sum of partials)) * gain); block 0 stores the new residual
+};
+enum GemvEpilogue {
+    EPI_STORE = 0,    // out[row * out_stride] = (weight dtype) acc          (tier-1 op, logits use EPI_F32)
+    EPI_F32 = 1,      // out[row] = acc as f32, unrounded (partials, logits)
+    EPI_QKV = 2,      // round, RoPE on q and k, write q buffer and KV cache
+    EPI_SWIGLU = 3,   // two matrices: gate[row] = round(silu(round(a1)) * round(a3))
+};
+
+#define RLB_MAX_TP 8
+
+struct GemvArgs {
+    // weights
+    const void* W = nullptr;   // [rows x K], row stride ldw elements
+    const void* W2 = nullptr;  // second matrix (w3) for EPI_SWIGLU
+    int rows = 0, K = 0;
+    int64_t ldw = 0;
+    // prologue
+    const void* vec_in = nullptr;    // PRO_COPY source (weight dtype)
+    const float* x_in = nullptr;     // PRO_NORM: residual stream (or embedding table when tok_ptr set)
+    const int32_t* tok_ptr = nullptr;  // PRO_NORM: if set, x row = x_in + tok * K
+    const float* parts = nullptr;    // PRO_NORM: n_parts partial sums of K floats, stride part_stride
+    int n_parts = 0;
+    int64_t part_stride = 0;
+    int round_parts = 0;             // round the summed partials to f16 before the residual add
+    float* x_out = nullptr;          // PRO_NORM: block 0 writes the updated residual here
+    const float* gain = nullptr;
+    float eps = 0.f;
+    // epilogue
+    void* out = nullptr;
+    int64_t out_stride = 1;
+    float* outs[RLB_MAX_TP] = {nullptr};  // EPI_F32 push mode: per-destination base pointers (may be peer memory)
+    int n_outs = 0;                  // 0: write `out` only
+    int64_t out_offset = 0;          // added to row for pushed writes
+    unsigned long long* flags[RLB_MAX_TP] = {nullptr};  // per-destination arrival counters (push mode)
+    // EPI_QKV
+    float* qbuf = nullptr;
+    void* kcache = nullptr;          // this layer's K cache [heads][max_seq][hd]
+    void* vcache = nullptr;
+    const float* rope = nullptr;     // [max_seq][hd/2][2]
+    const int32_t* pos_ptr = nullptr;
+    int nq = 0, hd = 0, max_seq = 0;
+};
+
+// dtype: weight (= activation) dtype. Chooses rows-per-warp and grid from the shape.
+int launch_gemv(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& args);
+// Tuning knobs (read once from the environment by gemv.cu): rows per warp, CTAs per SM.
+void gemv_set_tuning(int rows_per_warp, int ctas_per_sm, int threads);
+
+// ---------------------------------------------------------------------------------------
+// attention (attention.cu)
+// ---------------------------------------------------------------------------------------
+struct AttnDecodeArgs {
+    const float* q = nullptr;      // [heads][hd] f32, rotated
+    const void* kcache = nullptr;  // [heads][max_seq][hd]
+    const void* vcache = nullptr;
+    void* out = nullptr;           // [heads*hd] in the weight dtype (rounded when f16)
+    const int32_t* pos_ptr = nullptr;  // attends to positions 0..*pos_ptr
+    int heads = 0, hd = 0, max_seq = 0;
+    int n_split = 1;
+    float* scratch = nullptr;      // [heads][n_split][hd + 2] partial (o, m, l)
+    unsigned int* counters = nullptr;  // [heads], zero between launches
+};
+int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a);
+size_t attn_decode_scratch_floats(int heads, int hd, int n_split);
+
+struct AttnPrefillArgs {
+    const float* q = nullptr;      // [n][heads*hd] f32 rotated
+    const void* kcache = nullptr;
+    const void* vcache = nullptr;
+    void* out = nullptr;           // [n][heads*hd] weight dtype
+    int n = 0, start_pos = 0, heads = 0, hd = 0, max_seq = 0;
+};
+int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillArgs& a);
+
+// ---------------------------------------------------------------------------------------
+// row-wise / element-wise kernels used by prefill and the tier-1 ops (elementwise.cu)
+// ---------------------------------------------------------------------------------------
+int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, int n, int dim, float* x);
+// a[n][dim] (weight dtype) = cast(rmsnorm(x) * gain)
+int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype,
+                        void* out);
+// q,k,v: [n][nq] f32 GEMM outputs (already rounded when f16). Rotates q in place, writes K (rotated) and V to the cache.
+int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int n, int start_pos, int heads, int hd,
+                       int max_seq, const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache);
+// g[n][F] (weight dtype) = cast(silu(a1) * a3)
+int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t count, rlb_dtype out_dtype, void* out);
+// x[i] += round_f16?(y[i])
+int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int round_f16);
+int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok);
+// greedy feedback: tok <- argmax, pos <- pos + 1, tokens_out[step] <- tok, step <- step + 1
+int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
+                          int32_t* tokens_out, int32_t tokens_cap);
+int launch_convert(rlb_ctx* ctx, const void* src, rlb_dtype src_dtype, int64_t src_ld, void* dst, rlb_dtype dst_dtype,
+                   int64_t dst_ld, int64_t rows, int64_t cols);
+int launch_silu(rlb_ctx* ctx, void* t, rlb_dtype dtype, int64_t rows, int64_t cols, int64_t cap);
+int launch_hadamard(rlb_ctx* ctx, void* dst, const void* other, rlb_dtype dtype, int64_t rows, int64_t cols,
+                    int64_t dst_cap, int64_t other_cap);
+int launch_transpose(rlb_ctx* ctx, void* dst, const void* src, rlb_dtype dtype, int64_t dst_rows, int64_t dst_cols,
+                     int64_t dst_cap, int64_t src_cap);
+int launch_cache_shift_left(rlb_ctx* ctx, void* cache, rlb_dtype dtype, int64_t heads, int max_seq, int hd, int shifts);
+
+// ---------------------------------------------------------------------------------------
+// prefill GEMM (gemm.cu): C[n][M] f32 = A[n][K] * W[M][K]^T, optional f16 rounding of the result
+// ---------------------------------------------------------------------------------------
+int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, float* C,
+                   int64_t ldc, int n, int M, int K, int round_out);
+// Same contraction, output stored in the operand dtype (tier-1 op).
+int launch_gemm_nt_typed(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, void* C,
+                         int64_t ldc, int n, int M, int K);
+
+// ---------------------------------------------------------------------------------------
+// helpers
+// ---------------------------------------------------------------------------------------
+static inline void count_launch(rlb_ctx* ctx, uint64_t n = 1) { ctx->launches += n; }
+#define RLB_LAUNCH_CHECK()                                                                         \
+    do {                                                                                           \
+        cudaError_t _e = cudaGetLastError();                                                       \
+        if (_e != cudaSuccess)                                                                     \
+            return rlb_fail(RLB_ERR_CUDA, "kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e), \
+                            __FILE__, __LINE__);                                                   \
+    } while (0)

@@ -1,0 +1,193 @@
+"""Model-level parity of the CUDA path (through the C ABI) against the CPU oracle and the
+committed golden vectors. Bounds are BASELINE's: per-token logits within 1e-4 relative
+(max |delta| / max |logit|) for f32, within 2e-2 max-abs for f16, identical greedy tokens."""
+import os
+
+import numpy as np
+import pytest
+
+from rllama_b200 import RllamaError
+from rllama_b200 import synthetic as S
+from helpers import build_pair, cfg_variant, rel_err, top2_margin
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+F32_REL = 1e-4
+F16_ABS = 2e-2
+
+
+def greedy_protocol(model, prompt, steps, caches=None):
+    """Prefill at position 0, then `steps` single-token decodes (src/rllama_main.rs:821-901)."""
+    caches = caches or model.make_caches()
+    logits = [model.forward(prompt, 0, caches)]
+    tokens = []
+    for i in range(steps):
+        tokens.append(int(np.argmax(logits[-1])))
+        logits.append(model.forward([tokens[-1]], len(prompt) + i, caches))
+    return tokens, logits
+
+
+def test_tiny_f32_full_protocol_matches_oracle_and_golden(cuda_ctx):
+    cfg = S.CONFIGS["tiny"]
+    gpu, orc = build_pair(cfg, False, cuda_ctx, oracle_threads=4)
+    prompt = S.synth_tokens(cfg["prompt"], cfg["vocab"])
+    gt, gl = greedy_protocol(gpu, prompt, cfg["decode"])
+    ot, ol = greedy_protocol(orc, prompt, cfg["decode"])
+    worst = max(rel_err(a, b) for a, b in zip(gl, ol))
+    assert worst <= F32_REL, worst
+    assert gt == ot
+    g = np.load(os.path.join(GOLDEN, "golden_tiny_f32.npz"))
+    assert gt == g["tokens"].tolist()
+    for step in (0, 1, 64):
+        assert rel_err(gl[step], g["logits_step%d" % step]) <= F32_REL
+
+
+def test_tiny_f16_full_protocol(cuda_ctx):
+    cfg = S.CONFIGS["tiny"]
+    gpu, orc = build_pair(cfg, True, cuda_ctx, oracle_threads=4)
+    prompt = S.synth_tokens(cfg["prompt"], cfg["vocab"])
+    # teacher-forced on the oracle's tokens so that one near-tie cannot hide later steps
+    ot, ol = greedy_protocol(orc, prompt, cfg["decode"])
+    caches = gpu.make_caches()
+    gl = [gpu.forward(prompt, 0, caches)]
+    for i, tok in enumerate(ot):
+        gl.append(gpu.forward([tok], len(prompt) + i, caches))
+    worst = max(float(np.abs(a - b).max()) for a, b in zip(gl, ol))
+    assert worst <= F16_ABS, worst
+    for a, b in zip(gl, ol):
+        if int(np.argmax(a)) != int(np.argmax(b)):
+            # a different arg-max is only acceptable at a near-tie of the oracle's own logits
+            assert top2_margin(b) <= 2 * float(np.abs(a - b).max())
+    g = np.load(os.path.join(GOLDEN, "golden_tiny_f16.npz"))
+    assert float(np.abs(gl[0] - g["logits_step0"]).max()) <= F16_ABS
+    # free-running greedy sequence
+    gt, _ = greedy_protocol(gpu, prompt, cfg["decode"])
+    first_diff = next((i for i, (a, b) in enumerate(zip(gt, ot)) if a != b), None)
+    if first_diff is not None:
+        assert top2_margin(ol[first_diff]) <= 2 * worst, "greedy sequences diverge at step %d away from a near-tie" % first_diff
+
+
+@pytest.mark.parametrize("f16", [False, True])
+def test_7b_shape_two_layers(cuda_ctx, f16):
+    """Full 7B layer shapes (dim 4096, 32 heads, FFN 11008, vocab 32000) at reduced depth."""
+    cfg = cfg_variant("7b", n_layers=2, max_seq_len=48)
+    gpu, orc = build_pair(cfg, f16, cuda_ctx)
+    prompt = S.synth_tokens(24, cfg["vocab"])
+    ot, ol = greedy_protocol(orc, prompt, 6)
+    caches = gpu.make_caches()
+    gl = [gpu.forward(prompt, 0, caches)]
+    for i, tok in enumerate(ot):
+        gl.append(gpu.forward([tok], len(prompt) + i, caches))
+    if f16:
+        assert max(float(np.abs(a - b).max()) for a, b in zip(gl, ol)) <= F16_ABS
+    else:
+        assert max(rel_err(a, b) for a, b in zip(gl, ol)) <= F32_REL
+
+
+def test_odd_head_dim_and_ffn_shapes(cuda_ctx):
+    """head_dim 64 and 128, FFN widths that are not multiples of the tile sizes."""
+    for over in (dict(dim=256, n_heads=2, ffn=696, n_layers=2, vocab=1000), dict(dim=384, n_heads=6, ffn=1032, n_layers=1, vocab=512)):
+        cfg = cfg_variant("tiny", **over)
+        for f16 in (False, True):
+            gpu, orc = build_pair(cfg, f16, cuda_ctx)
+            prompt = S.synth_tokens(5, cfg["vocab"])
+            ot, ol = greedy_protocol(orc, prompt, 3)
+            caches = gpu.make_caches()
+            gl = [gpu.forward(prompt, 0, caches)]
+            for i, tok in enumerate(ot):
+                gl.append(gpu.forward([tok], len(prompt) + i, caches))
+            if f16:
+                assert max(float(np.abs(a - b).max()) for a, b in zip(gl, ol)) <= F16_ABS
+            else:
+                assert max(rel_err(a, b) for a, b in zip(gl, ol)) <= F32_REL
+
+
+def test_single_token_prompt_and_last_position(cuda_ctx):
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, max_seq_len=8)
+    gpu, orc = build_pair(cfg, False, cuda_ctx)
+    gc, oc = gpu.make_caches(), orc.make_caches()
+    tok = 7
+    for pos in range(8):  # decode from an empty cache up to the maximum sequence length
+        a, b = gpu.forward([tok], pos, gc), orc.forward([tok], pos, oc)
+        assert rel_err(a, b) <= F32_REL
+        tok = int(np.argmax(b))
+    with pytest.raises(RllamaError):
+        gpu.forward([tok], 8, gc)
+
+
+def test_prefill_equals_token_by_token_and_chunked(cuda_ctx):
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000)
+    gpu, _ = build_pair(cfg, False, cuda_ctx, with_oracle=False)
+    toks = S.synth_tokens(11, cfg["vocab"])
+    full = gpu.forward(toks, 0, gpu.make_caches())
+    c = gpu.make_caches()
+    for i, t in enumerate(toks):
+        step = gpu.forward([int(t)], i, c)
+    assert rel_err(step, full) <= F32_REL
+    # a multi-token call at start_pos > 0 (the reference panics there) is a causal chunk
+    c2 = gpu.make_caches()
+    gpu.forward(toks[:4], 0, c2)
+    chunked = gpu.forward(toks[4:], 4, c2)
+    assert rel_err(chunked, full) <= F32_REL
+
+
+def test_device_greedy_loop_equals_host_loop(cuda_ctx):
+    cfg = cfg_variant("tiny", n_layers=3, vocab=4000)
+    for f16 in (False, True):
+        gpu, _ = build_pair(cfg, f16, cuda_ctx, with_oracle=False)
+        prompt = S.synth_tokens(9, cfg["vocab"])
+        host_tokens, _ = greedy_protocol(gpu, prompt, 20)
+        c = gpu.make_caches()
+        first = gpu.forward_greedy(prompt, 0, c)
+        assert first == host_tokens[0]
+        dev_tokens, ms = gpu.decode_greedy(first, len(prompt), 19, c)
+        assert dev_tokens.tolist() == host_tokens[1:20]
+        assert ms > 0.0
+        assert gpu.get_stat("kernels_per_step") == 5 * cfg["n_layers"] + 2
+
+
+def test_cache_contents_clone_and_shift(cuda_ctx):
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, max_seq_len=16)
+    gpu, orc = build_pair(cfg, True, cuda_ctx)
+    toks = S.synth_tokens(6, cfg["vocab"])
+    gc, oc = gpu.make_caches(), orc.make_caches()
+    gpu.forward(toks, 0, gc); orc.forward(toks, 0, oc)
+    hd = cfg["dim"] // cfg["n_heads"]
+    for which in ("k", "v"):
+        for pos in (0, 5):
+            got = gc.read(which, 1, 3, pos)
+            want = np.array([oc.get(which, 1, 3, d, pos) for d in range(hd)], dtype=np.float32)
+            assert np.abs(got - want).max() <= 2e-3  # f16-rounded values, one ulp apart at most
+    assert np.all(gc.read("k", 1, 3, 6) == 0.0)  # Tensor::zeros beyond the written prefix
+    clone = gc.true_clone()
+    nxt = 11
+    a = gpu.forward([nxt], 6, gc)
+    assert np.all(clone.read("k", 0, 0, 6) == 0.0)  # the clone is independent
+    b = gpu.forward([nxt], 6, clone)
+    assert np.array_equal(a, b)
+    before = [gc.read("v", 0, 2, p).copy() for p in range(16)]
+    gc.shift_left(2)
+    for p in range(14):
+        assert np.array_equal(gc.read("v", 0, 2, p), before[p + 2])
+    assert np.array_equal(gc.read("v", 0, 2, 15), before[15]) and np.array_equal(gc.read("v", 0, 2, 14), before[15])
+
+
+def test_construction_errors(cuda_ctx):
+    from rllama_b200 import DataSettings, Transformer
+    cfg = cfg_variant("tiny", n_layers=1, vocab=1000)
+    m = Transformer(cfg["dim"], 1, cfg["n_heads"], cfg["ffn"], cfg["vocab"], 16, 1e-6, DataSettings(cl=cuda_ctx))
+    with pytest.raises(RllamaError):  # MissingField
+        m.finalize()
+    with pytest.raises(RllamaError):
+        m.set_tensor("wq", 0, np.zeros((cfg["dim"], cfg["dim"] + 16), np.float16))
+    with pytest.raises(RllamaError):
+        m.set_tensor("wq", 5, np.zeros((cfg["dim"], cfg["dim"]), np.float16))
+    with pytest.raises(RllamaError):
+        Transformer(100, 1, 3, 64, 100, 16, 1e-6, DataSettings(cl=cuda_ctx))
+    S.load_into(m, cfg)
+    m.finalize()
+    c = m.make_caches()
+    with pytest.raises(RllamaError):
+        m.forward([1000], 0, c)
+    with pytest.raises(RllamaError):
+        m.forward(list(range(17)), 0, c)

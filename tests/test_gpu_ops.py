@@ -1,0 +1,107 @@
+"""Op-level parity of the CUDA backend against the CPU oracle: the reference's
+``#[cfg(feature = "opencl")]`` tests (rllama ``src/tensor.rs:2922-3208``) with seeded inputs,
+same shapes and tolerances, plus the f32 variants the CUDA backend adds."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from rllama_b200 import F16, F32, RllamaError
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_close(a, b, eps):
+    a = np.asarray(a, dtype=np.float64); b = np.asarray(b, dtype=np.float64)
+    return bool((np.abs(a - b) <= eps).all())
+
+
+def gpu_mmt(ctx, x, y):
+    a, b = ctx.upload(x), ctx.upload(y)
+    c = ctx.zeros(x.shape[0], y.shape[0], F16 if x.dtype == np.float16 else F32)
+    c.matrix_mul_inplace_transposed(a, b)
+    out = c.to_numpy()
+    for t in (a, b, c):
+        t.free()
+    return out
+
+
+def test_matrix_mul_transposed_512x1024_768x1024(cuda_ctx):
+    # src/tensor.rs:2922-2951 (1e-1 against the f32 CPU result)
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, (512, 1024)).astype(np.float32); y = rng.uniform(-1, 1, (768, 1024)).astype(np.float32)
+    want = O.matrix_mul_transposed(x, y, nthreads=4)
+    got = gpu_mmt(cuda_ctx, x.astype(np.float16), y.astype(np.float16)).astype(np.float32)
+    assert rel_close(got, want, 1e-1)
+    got32 = gpu_mmt(cuda_ctx, x, y)
+    assert np.abs(got32 - want).max() <= 1e-4 * np.abs(want).max()
+
+
+def test_matrix_mul_transposed_1024_square(cuda_ctx):
+    # src/tensor.rs:2954-2983
+    rng = np.random.default_rng(1)
+    x = rng.uniform(-1, 1, (1024, 1024)).astype(np.float16); y = rng.uniform(-1, 1, (1024, 1024)).astype(np.float16)
+    want = O.matrix_mul_transposed(x, y, nthreads=4).astype(np.float32)
+    got = gpu_mmt(cuda_ctx, x, y).astype(np.float32)
+    assert rel_close(got, want, 1e-1)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_matrix_mul_transposed_random_sizes(cuda_ctx, dtype):
+    # src/tensor.rs:2986-3090: sizes up to 300, including one row on either side; 1e-2
+    rng = np.random.default_rng(2)
+    shapes = [(int(a), int(b), int(c)) for a, b, c in rng.integers(1, 300, size=(40, 3))]
+    shapes += [(1, int(b), int(c)) for b, c in rng.integers(1, 300, size=(20, 2))]
+    shapes += [(int(a), int(b), 1) for a, b in rng.integers(1, 300, size=(20, 2))]
+    shapes += [(1, 7, 1), (1, 300, 300), (300, 1, 300), (4, 16, 4)]
+    for a, b, c in shapes:
+        x = rng.uniform(-1, 1, (a, b)).astype(dtype); y = rng.uniform(-1, 1, (c, b)).astype(dtype)
+        want = O.matrix_mul_transposed(x, y).astype(np.float32)
+        got = gpu_mmt(cuda_ctx, x, y).astype(np.float32)
+        assert got.shape == want.shape
+        assert rel_close(got, want, 1e-2 if dtype == np.float16 else 1e-4), (a, b, c)
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_silu_hadamard_transpose_copy(cuda_ctx, dtype):
+    # src/tensor.rs:3093-3208, 1e-2 (f16)
+    rng = np.random.default_rng(3)
+    tol = 1e-2 if dtype == np.float16 else 1e-6
+    for _ in range(20):
+        r, c = (int(v) for v in rng.integers(1, 300, size=2))
+        x = rng.uniform(-1, 1, (r, c)).astype(dtype); y = rng.uniform(-1, 1, (r, c)).astype(dtype)
+        t = cuda_ctx.upload(x); t.silu_inplace()
+        assert rel_close(t.to_numpy().astype(np.float32), O.silu(x.astype(np.float32)).reshape(r, c), tol)
+        t2 = cuda_ctx.upload(x); u = cuda_ctx.upload(y); t2.hadamard_product_inplace(u)
+        assert rel_close(t2.to_numpy().astype(np.float32), x.astype(np.float32) * y.astype(np.float32), tol)
+        tt = cuda_ctx.zeros(c, r, F16 if dtype == np.float16 else F32); tt.transpose_from(u)
+        assert np.array_equal(tt.to_numpy(), y.T)
+        cp = cuda_ctx.zeros(r, c, F16 if dtype == np.float16 else F32); cp.copy_inplace(u)
+        assert np.array_equal(cp.to_numpy(), y)
+        for h in (t, t2, u, tt, cp):
+            h.free()
+
+
+def test_f16_result_is_a_rounded_f32_accumulation(cuda_ctx):
+    """f16 operands: exact products, f32 accumulation, one RNE rounding of the result
+    (src/tensor.rs:1476-1666) -- so the GPU may differ from the oracle by summation order
+    only, i.e. by at most one f16 ulp of the result."""
+    rng = np.random.default_rng(4)
+    x = (rng.normal(0, 1, (1, 4096))).astype(np.float16); w = (rng.normal(0, 0.02, (512, 4096))).astype(np.float16)
+    want = O.matrix_mul_transposed(x, w)
+    got = gpu_mmt(cuda_ctx, x, w)
+    ulp = np.spacing(np.abs(want).astype(np.float16)).astype(np.float32)
+    assert (np.abs(got.astype(np.float32) - want.astype(np.float32)) <= ulp).all()
+    assert (got.view(np.uint16) == want.view(np.uint16)).mean() > 0.97
+
+
+def test_shape_and_dtype_errors(cuda_ctx):
+    a = cuda_ctx.upload(np.zeros((4, 8), np.float32)); b = cuda_ctx.upload(np.zeros((4, 9), np.float32))
+    c = cuda_ctx.zeros(4, 4, F32)
+    with pytest.raises(RllamaError):  # "Invalid matrix multiplication" (src/tensor.rs:1261-1266)
+        c.matrix_mul_inplace_transposed(a, b)
+    h = cuda_ctx.upload(np.zeros((4, 8), np.float16))
+    with pytest.raises(RllamaError):  # different dtypes (:1267-1272)
+        c.matrix_mul_inplace_transposed(a, h)
+    with pytest.raises(RllamaError):
+        a.hadamard_product_inplace(b)
+    assert cuda_ctx.kernel_launches() > 0
