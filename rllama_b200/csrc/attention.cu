@@ -150,6 +150,10 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnDecodeA
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[kWarps];
     __shared__ unsigned int ticket_sh;
+    // programmatic dependent launch: let the next kernel (the wo projection) start streaming its
+    // weights now; wait for the q/k/v kernel before touching its outputs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int hd = a.hd, head = blockIdx.x, split = blockIdx.y, ns = a.n_split;
     const int T = *a.pos_ptr + 1;
     int chunk = (T + ns - 1) / ns;
@@ -229,7 +233,7 @@ size_t attn_smem_bytes(int hd, int vec, int max_positions) {
 
 size_t attn_decode_scratch_floats(int heads, int hd, int n_split) { return (size_t)heads * n_split * (hd + 2); }
 
-int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a) {
+int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a, int allow_pdl) {
     const int vec = cache_dtype == RLB_F16 ? 8 : 4;
     if (a.hd % 8 != 0 || (a.hd / 8) % vec != 0 || a.hd / vec > kThreads)
         return rlb_fail(RLB_ERR_INVALID, "attention: head_dim %d is not supported", a.hd);
@@ -237,17 +241,25 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
     chunk = (chunk + 31) & ~31;
     const size_t smem = attn_smem_bytes(a.hd, vec, chunk);
     if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "attention: %d positions per CTA do not fit in shared memory", chunk);
-    dim3 grid(a.heads, a.n_split);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(a.heads, a.n_split);
+    lc.blockDim = dim3(kThreads);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = allow_pdl ? 1 : 0;
     if (cache_dtype == RLB_F16) {
         static bool set = false;
         if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
-        attn_decode_kernel<__half><<<grid, kThreads, smem, ctx->stream>>>(a);
+        RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_kernel<__half>, a));
     } else {
         static bool set = false;
         if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
-        attn_decode_kernel<float><<<grid, kThreads, smem, ctx->stream>>>(a);
+        RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_kernel<float>, a));
     }
-    RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
 }

@@ -1,0 +1,447 @@
+// Decode GEMV with the weight stream staged through shared memory by the bulk-copy engine.
+//
+// Same contraction, prologues and epilogues as gemv.cu (rllama's one-row
+// Tensor::matrix_mul_transposed, src/tensor.rs:999-1025, :1250-1668), different data path:
+// a GEMV at batch 1 is bound by how many bytes are in flight, and register-staged loads
+// leave that to the compiler's scheduling. Here one producer warp issues `cp.async.bulk`
+// copies (global -> shared, completion counted on an mbarrier) of RB weight rows x KC
+// columns per stage into a ring of up to 12 stages (up to ~190 KB in flight per SM), and
+// eight consumer warps read the stages from shared memory. The producer starts before the
+// kernel waits for its predecessor (programmatic dependent launch): weights do not depend
+// on the previous kernel, so the ring is already full when the activation row arrives.
+//
+// Work split: a CTA owns whole row tiles (RB rows x all of K); inside a tile the eight
+// consumer warps split K. Their per-lane partial sums go through shared memory to a tenth
+// warp that folds them in a fixed order and runs the fused epilogue, so the consumers never
+// stop at a CTA-wide barrier and results do not depend on the grid size.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out the kernel raises an error flag
+// in global memory, switches to a mode in which no wait blocks, and runs to its end.
+#include "internal.h"
+
+#include <cstdlib>
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 64;  // + one producer warp + one epilogue warp
+constexpr int kPartialDepth = 2;           // tiles the epilogue warp may lag behind
+constexpr int kMaxStages = 12;
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+template <typename T> struct Vec;
+template <> struct Vec<__half> { static constexpr int N = 8; };
+template <> struct Vec<float> { static constexpr int N = 4; };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait. Returns immediately once the CTA is in "dead" mode.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead, int* err) {
+    for (uint32_t i = 0; i < kWaitLimit; i++) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((i & 255u) == 255u && *dead) return;
+    }
+    *dead = 1;
+    atomicExch(err, 1);
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+template <typename T> __device__ __forceinline__ T cast_to(float v);
+template <> __device__ __forceinline__ __half cast_to<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float cast_to<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ float maybe_round(float v);
+template <> __device__ __forceinline__ float maybe_round<__half>(float v) { return round_f16(v); }
+template <> __device__ __forceinline__ float maybe_round<float>(float v) { return v; }
+
+template <typename T> __device__ __forceinline__ void unpack(const uint4& v, float (&f)[Vec<T>::N]);
+template <> __device__ __forceinline__ void unpack<__half>(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+template <> __device__ __forceinline__ void unpack<float>(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+struct StreamCfg {
+    int n_stages;
+    int* err;
+};
+
+template <typename WT, int RB, int J, int PRO, int EPI>
+__global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs a, const StreamCfg cfg) {
+    constexpr int VEC = Vec<WT>::N;
+    constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int SL = J * 32 * VEC;               // K elements one warp covers per stage
+    constexpr int KC = kConsumerWarps * SL;        // K elements per stage
+    constexpr int NSEG = NMAT * RB;                // row segments per stage
+    constexpr int STAGE_ELEMS = NSEG * KC;
+    constexpr size_t STAGE_BYTES = (size_t)STAGE_ELEMS * sizeof(WT);
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int K = a.K, S = cfg.n_stages;
+    WT* ring = reinterpret_cast<WT*>(smem_raw);
+    unsigned char* p = smem_raw + (size_t)S * STAGE_BYTES;
+    WT* act = reinterpret_cast<WT*>(p);
+    p += (((size_t)K * sizeof(WT)) + 15) & ~(size_t)15;
+    float* tmp = reinterpret_cast<float*>(p);
+    if (PRO == PRO_NORM) p += (size_t)K * sizeof(float);
+    float* partial = reinterpret_cast<float*>(p);  // [kPartialDepth][NSEG][kConsumers]
+    p += sizeof(float) * kPartialDepth * NSEG * kConsumers;
+    float* red = reinterpret_cast<float*>(p);
+    p += sizeof(float) * kConsumerWarps;
+    p = reinterpret_cast<unsigned char*>(((uintptr_t)p + 7) & ~(uintptr_t)7);
+    uint64_t* full = reinterpret_cast<uint64_t*>(p);
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* pfull = empty + kMaxStages;       // [kPartialDepth] consumers -> epilogue warp
+    uint64_t* pempty = pfull + kPartialDepth;   // [kPartialDepth] epilogue warp -> consumers
+    __shared__ int dead_flag;
+    volatile int* dead = &dead_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        dead_flag = 0;
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        for (int s = 0; s < kPartialDepth; s++) {
+            mbar_init(&pfull[s], kConsumerWarps);
+            mbar_init(&pempty[s], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const int n_tiles = a.rows / RB;
+    const WT* W_a = reinterpret_cast<const WT*>(a.W);
+    const WT* W_b = reinterpret_cast<const WT*>(a.W2);
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer warp -------------------------------------
+        int s = 0;
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int row0 = tile * RB;
+            for (int k0 = 0; k0 < K; k0 += KC) {
+                mbar_wait(&empty[s], ph ^ 1u, dead, cfg.err);
+                const int kn = min(KC, K - k0);
+                const uint32_t nbytes = (uint32_t)kn * sizeof(WT);
+                if (lane == 0) mbar_expect_tx(&full[s], nbytes * NSEG);
+                __syncwarp();
+                if (lane < NSEG && !*dead) {
+                    const int m = lane / RB, r = lane - m * RB;
+                    bulk_g2s(ring + (size_t)s * STAGE_ELEMS + (size_t)lane * KC, (m == 0 ? W_a : W_b) + (int64_t)(row0 + r) * a.ldw + k0,
+                             nbytes, &full[s]);
+                }
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+        return;
+    }
+
+    pdl_wait();  // everything below reads or overwrites what earlier kernels use
+
+    if (warp == kConsumerWarps + 1) {
+        // ------------------------------ epilogue warp -------------------------------------
+        int ps = 0;
+        uint32_t pph = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int row0 = tile * RB;
+            mbar_wait(&pfull[ps], pph, dead, cfg.err);
+            const float* pp = partial + (size_t)ps * NSEG * kConsumers;
+            float tot[NSEG];
+#pragma unroll
+            for (int i = 0; i < NSEG; i++) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; w++) t += pp[i * kConsumers + w * 32 + lane];  // fixed order
+                tot[i] = warp_sum(t);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pempty[ps]);
+            if (++ps == kPartialDepth) { ps = 0; pph ^= 1u; }
+            auto total = [&](int i) {
+                float t = tot[0];
+#pragma unroll
+                for (int q = 1; q < NSEG; q++) t = (i == q) ? tot[q] : t;
+                return t;
+            };
+            if (EPI == EPI_STORE) {
+                if (lane < RB) reinterpret_cast<WT*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = cast_to<WT>(total(lane));
+            } else if (EPI == EPI_F32) {
+                if (lane < RB) {
+                    const float v = total(lane);
+                    if (a.n_outs == 0) {
+                        reinterpret_cast<float*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = v;
+                    } else {
+                        for (int d = 0; d < a.n_outs; d++) a.outs[d][a.out_offset + row0 + lane] = v;
+                    }
+                }
+            } else if (EPI == EPI_SWIGLU) {
+                if (lane < RB) {
+                    const float a1 = maybe_round<WT>(total(lane));
+                    const float a3 = maybe_round<WT>(total(RB + lane));
+                    const float sg = a1 / (1.0f + expf(-a1));
+                    reinterpret_cast<WT*>(a.out)[row0 + lane] = cast_to<WT>(__fmul_rn(sg, a3));
+                }
+            } else if (EPI == EPI_QKV) {
+                if (lane < RB / 2) {
+                    const int pos = *a.pos_ptr;
+                    const int row = row0 + 2 * lane;
+                    const int sec = row / a.nq, rr = row - sec * a.nq;
+                    const int head = rr / a.hd, c = rr - head * a.hd;
+                    const float re = maybe_round<WT>(total(2 * lane));
+                    const float im = maybe_round<WT>(total(2 * lane + 1));
+                    const float* f = a.rope + ((int64_t)pos * (a.hd / 2) + (c >> 1)) * 2;
+                    const float fr = f[0], fi = f[1];
+                    const float o_re = __fsub_rn(__fmul_rn(re, fr), __fmul_rn(im, fi));  // src/transformer.rs:844-847
+                    const float o_im = __fadd_rn(__fmul_rn(re, fi), __fmul_rn(im, fr));
+                    if (sec == 0) {
+                        a.qbuf[rr] = o_re;
+                        a.qbuf[rr + 1] = o_im;
+                    } else {
+                        WT* cache = reinterpret_cast<WT*>(sec == 1 ? a.kcache : a.vcache);
+                        WT* dst = cache + ((int64_t)head * a.max_seq + pos) * a.hd + c;
+                        dst[0] = cast_to<WT>(sec == 1 ? o_re : re);
+                        dst[1] = cast_to<WT>(sec == 1 ? o_im : im);
+                    }
+                }
+            }
+        }
+        if (EPI == EPI_F32 && a.n_outs > 0 && a.flags[0] != nullptr) {
+            // push mode: this warp made all of the CTA's remote stores
+            __threadfence_system();
+            __syncwarp();
+            if (lane < a.n_outs) atomicAdd_system(a.flags[lane], 1ull);
+        }
+        return;
+    }
+
+    // -------------------------------- consumer warps ---------------------------------------
+    if (PRO == PRO_COPY) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.vec_in);
+        uint4* dst = reinterpret_cast<uint4*>(act);
+        for (int i = tid; i < K / VEC; i += kConsumers) dst[i] = src[i];
+    } else {
+        const float* xin = a.x_in;
+        if (a.tok_ptr) xin += (int64_t)(*a.tok_ptr) * K;
+        float ss = 0.f;
+        for (int i = tid * 4; i < K; i += kConsumers * 4) {
+            float4 v = *reinterpret_cast<const float4*>(xin + i);
+            if (a.n_parts > 0) {
+                float4 sacc = *reinterpret_cast<const float4*>(a.parts + i);
+                for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
+                    const float4 t = *reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i);
+                    sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
+                }
+                if (a.round_parts) {
+                    sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
+                }
+                v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+            }
+            *reinterpret_cast<float4*>(tmp + i) = v;
+            if (blockIdx.x == 0 && a.x_out) *reinterpret_cast<float4*>(a.x_out + i) = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        consumer_sync();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
+        const float scale = 1.0f / sqrtf(tot / (float)K + a.eps);
+        for (int i = tid; i < K; i += kConsumers) act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), a.gain[i]));
+    }
+    consumer_sync();
+
+    int s = 0, ps = 0;
+    uint32_t ph = 0, pph = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        float acc[NSEG];
+#pragma unroll
+        for (int i = 0; i < NSEG; i++) acc[i] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += KC) {
+            mbar_wait(&full[s], ph, dead, cfg.err);
+            const WT* st = ring + (size_t)s * STAGE_ELEMS;
+#pragma unroll
+            for (int j = 0; j < J; j++) {
+                const int kk = warp * SL + (j * 32 + lane) * VEC;
+                if (k0 + kk < K) {
+                    float af[VEC];
+                    unpack<WT>(*reinterpret_cast<const uint4*>(act + k0 + kk), af);
+#pragma unroll
+                    for (int i = 0; i < NSEG; i++) {
+                        float wf[VEC];
+                        unpack<WT>(*reinterpret_cast<const uint4*>(st + (size_t)i * KC + kk), wf);
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) acc[i] = fmaf(wf[e], af[e], acc[i]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == S) { s = 0; ph ^= 1u; }
+        }
+        // hand the per-lane partial sums of this tile to the epilogue warp
+        mbar_wait(&pempty[ps], pph ^ 1u, dead, cfg.err);
+        float* mine = partial + (size_t)ps * NSEG * kConsumers + tid;
+#pragma unroll
+        for (int i = 0; i < NSEG; i++) mine[i * kConsumers] = acc[i];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pfull[ps]);
+        if (++ps == kPartialDepth) { ps = 0; pph ^= 1u; }
+    }
+}
+
+struct StreamTuning {
+    bool loaded = false;
+    int stage_kb = 32;   // 16, 32 or 64
+    int max_stages = kMaxStages;
+    int pdl = 1;
+    int j2 = 0;          // prefer two vectors per lane and half the rows
+    int rb = 0;          // explicit rows per tile (0 = from stage_kb)
+    int smem_kb = 192;   // shared memory per CTA; the rest of the SM stays free for small co-resident CTAs
+} g_st;
+
+void load_tuning() {
+    if (g_st.loaded) return;
+    g_st.loaded = true;
+    if (const char* s = getenv("RLB_STREAM_STAGE_KB")) { int v = atoi(s); g_st.stage_kb = v >= 64 ? 64 : v >= 32 ? 32 : 16; }
+    if (const char* s = getenv("RLB_STREAM_STAGES")) { int v = atoi(s); if (v >= 2 && v <= kMaxStages) g_st.max_stages = v; }
+    if (const char* s = getenv("RLB_STREAM_PDL")) g_st.pdl = atoi(s) != 0;
+    if (const char* s = getenv("RLB_STREAM_J2")) g_st.j2 = atoi(s) != 0;
+    if (const char* s = getenv("RLB_STREAM_RB")) g_st.rb = atoi(s);
+    if (const char* s = getenv("RLB_STREAM_SMEM_KB")) { int v = atoi(s); if (v >= 48 && v <= 224) g_st.smem_kb = v; }
+}
+
+template <typename WT, int RB, int J, int PRO, int EPI>
+int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
+    constexpr int VEC = Vec<WT>::N;
+    constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr size_t STAGE_BYTES = (size_t)NMAT * RB * J * 8 * 32 * VEC * sizeof(WT);
+    auto kern = gemv_stream_kernel<WT, RB, J, PRO, EPI>;
+    size_t fixed = (((size_t)a.K * sizeof(WT)) + 15) & ~(size_t)15;
+    if (PRO == PRO_NORM) fixed += (size_t)a.K * sizeof(float);
+    fixed += sizeof(float) * kPartialDepth * NMAT * RB * kConsumers + sizeof(float) * kConsumerWarps + 16 +
+             (2 * kMaxStages + 2 * kPartialDepth) * sizeof(uint64_t);
+    const size_t budget = (size_t)g_st.smem_kb * 1024;
+    if (fixed + 2 * STAGE_BYTES > budget) return rlb_fail(RLB_ERR_LIMIT, "gemv: activation row of %d elements leaves no room for the weight ring", a.K);
+    int stages = (int)((budget - fixed) / STAGE_BYTES);
+    if (stages > g_st.max_stages) stages = g_st.max_stages;
+    const size_t smem = fixed + (size_t)stages * STAGE_BYTES;
+    static bool attr_set = false;
+    if (!attr_set) {
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        attr_set = true;
+    }
+    const int n_tiles = a.rows / RB;
+    int grid = n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
+    StreamCfg cfg;
+    cfg.n_stages = stages;
+    cfg.err = err_flag;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(kThreads);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = pdl ? 1 : 0;
+    RLB_CUDA(cudaLaunchKernelEx(&lc, kern, a, cfg));
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+template <typename WT, int PRO, int EPI>
+int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
+    load_tuning();
+    constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    const int unit = (EPI == EPI_QKV) ? a.nq : a.rows;
+    // stage = NMAT * RB * J * 4 KB
+    const int J = g_st.j2 ? 2 : 1;
+    int RB = g_st.rb > 0 ? g_st.rb / NMAT : g_st.stage_kb / 4 / NMAT / J;
+    if (RB > 8) RB = 8;
+    if (RB < 1) RB = 1;
+    while (RB > 1 && (unit % RB != 0 || a.rows % RB != 0)) RB >>= 1;
+    if (EPI == EPI_QKV && RB < 2) return rlb_fail(RLB_ERR_INVALID, "gemv: q/k/v projection needs an even number of rows per head");
+    if (J == 1) {
+        switch (RB) {
+            case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI>(ctx, a, err_flag, pdl);
+            case 4: return launch_cfg<WT, 4, 1, PRO, EPI>(ctx, a, err_flag, pdl);
+            case 2: return launch_cfg<WT, 2, 1, PRO, EPI>(ctx, a, err_flag, pdl);
+            default: break;
+        }
+    } else {
+        switch (RB) {
+            case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 2, PRO, EPI>(ctx, a, err_flag, pdl);
+            case 4: return launch_cfg<WT, 4, 2, PRO, EPI>(ctx, a, err_flag, pdl);
+            case 2: return launch_cfg<WT, 2, 2, PRO, EPI>(ctx, a, err_flag, pdl);
+            default: break;
+        }
+    }
+    return RLB_ERR_STATE;  // caller falls back to the register-staged kernel
+}
+
+template <typename WT>
+int launch_typed(rlb_ctx* ctx, int prologue, int epilogue, const GemvArgs& a, int* err_flag, bool pdl) {
+    if (prologue == PRO_NORM && epilogue == EPI_QKV) return launch_shape<WT, PRO_NORM, EPI_QKV>(ctx, a, err_flag, pdl);
+    if (prologue == PRO_NORM && epilogue == EPI_SWIGLU) return launch_shape<WT, PRO_NORM, EPI_SWIGLU>(ctx, a, err_flag, pdl);
+    if (prologue == PRO_NORM && epilogue == EPI_F32) return launch_shape<WT, PRO_NORM, EPI_F32>(ctx, a, err_flag, pdl);
+    if (prologue == PRO_COPY && epilogue == EPI_F32) return launch_shape<WT, PRO_COPY, EPI_F32>(ctx, a, err_flag, pdl);
+    return RLB_ERR_STATE;
+}
+
+}  // namespace
+
+// Returns RLB_ERR_STATE (without recording an error message) when the shape is not handled
+// here, so that the caller can use the register-staged kernel instead.
+int launch_gemv_stream(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a, int* err_flag, int allow_pdl) {
+    load_tuning();
+    const int vec = dtype == RLB_F16 ? 8 : 4;
+    if (a.K <= 0 || a.rows < 2 || a.K % vec != 0 || a.ldw % vec != 0 || (prologue == PRO_NORM && a.K % 4 != 0)) return RLB_ERR_STATE;
+    if ((a.ldw * (int64_t)(dtype == RLB_F16 ? 2 : 4)) % 16 != 0) return RLB_ERR_STATE;  // bulk copies need 16-byte aligned rows
+    const bool pdl = allow_pdl && g_st.pdl;
+    return dtype == RLB_F16 ? launch_typed<__half>(ctx, prologue, epilogue, a, err_flag, pdl)
+                            : launch_typed<float>(ctx, prologue, epilogue, a, err_flag, pdl);
+}

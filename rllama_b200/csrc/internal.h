@@ -111,6 +111,9 @@ struct GemvArgs {
 
 // dtype: weight (= activation) dtype. Chooses rows-per-warp and grid from the shape.
 int launch_gemv(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& args);
+// Bulk-copy staged variant (gemv_stream.cu). Returns RLB_ERR_STATE, without an error message,
+// for shapes it does not handle. err_flag: device int raised when a bounded wait ran out.
+int launch_gemv_stream(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& args, int* err_flag, int allow_pdl);
 // Tuning knobs (read once from the environment by gemv.cu): rows per warp, CTAs per SM.
 void gemv_set_tuning(int rows_per_warp, int ctas_per_sm, int threads);
 
@@ -128,7 +131,7 @@ struct AttnDecodeArgs {
     float* scratch = nullptr;      // [heads][n_split][hd + 2] partial (o, m, l)
     unsigned int* counters = nullptr;  // [heads], zero between launches
 };
-int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a);
+int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a, int allow_pdl);
 size_t attn_decode_scratch_floats(int heads, int hd, int n_split);
 
 struct AttnPrefillArgs {

@@ -99,6 +99,8 @@ struct rlb_model {
 
     // options / statistics
     bool use_graph = true;
+    bool use_stream = true;  // bulk-copy staged GEMV kernels (gemv_stream.cu)
+    bool use_pdl = true;     // programmatic dependent launch between the decode kernels
     bool profile = false;
     double prof_ms[PC_COUNT] = {0};
     int prof_steps = 0;
@@ -165,6 +167,15 @@ int tp_reduce(rlb_model* m, float* part, size_t count) {
     return nccl_allreduce_f32(&m->nccl, part, count, m->ctx->stream);
 }
 
+// Decode GEMV: the bulk-copy staged kernel where the shape allows, else the register-staged one.
+int gemv_decode(rlb_model* m, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a) {
+    if (m->use_stream) {
+        const int s = launch_gemv_stream(m->ctx, dtype, prologue, epilogue, a, m->scalars + 8, m->use_pdl && !m->profile);
+        if (s != RLB_ERR_STATE) return s;
+    }
+    return launch_gemv(m->ctx, dtype, prologue, epilogue, a);
+}
+
 // ---- the decode step (enqueue only; runs eagerly or under stream capture) -----------------
 int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     rlb_ctx* ctx = m->ctx;
@@ -185,7 +196,7 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             a.qbuf = m->qbuf; a.kcache = kc; a.vcache = vc; a.rope = m->rope; a.pos_ptr = pos;
             a.nq = m->nq; a.hd = m->hd; a.max_seq = m->p.max_seq_len;
             prof_mark(m, PC_QKV);
-            RLB_TRY(launch_gemv(ctx, m->wdt, PRO_NORM, EPI_QKV, a));
+            RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_QKV, a));
         }
         {   // 2. attention
             AttnDecodeArgs a;
@@ -193,13 +204,13 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             a.heads = m->nh; a.hd = m->hd; a.max_seq = m->p.max_seq_len; a.n_split = m->n_split;
             a.scratch = m->attn_scratch; a.counters = m->attn_counters;
             prof_mark(m, PC_ATTN);
-            RLB_TRY(launch_attn_decode(ctx, m->wdt, a));
+            RLB_TRY(launch_attn_decode(ctx, m->wdt, a, m->use_stream && m->use_pdl && !m->profile));
         }
         {   // 3. wo
             GemvArgs a;
             a.W = W.wo; a.rows = d; a.K = m->nq; a.ldw = m->nq; a.vec_in = m->obuf; a.out = m->part_wo;
             prof_mark(m, PC_WO);
-            RLB_TRY(launch_gemv(ctx, m->wdt, PRO_COPY, EPI_F32, a));
+            RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
             RLB_TRY(tp_reduce(m, m->part_wo, d));
         }
         {   // 4. residual + norm + w1/w3 + SiLU gate
@@ -208,13 +219,13 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             a.x_in = m->xa; a.parts = m->part_wo; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
             a.x_out = m->xb; a.gain = W.ffn_norm; a.eps = m->p.norm_eps; a.out = m->gbuf;
             prof_mark(m, PC_W13);
-            RLB_TRY(launch_gemv(ctx, m->wdt, PRO_NORM, EPI_SWIGLU, a));
+            RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_SWIGLU, a));
         }
         {   // 5. w2
             GemvArgs a;
             a.W = W.w2; a.rows = d; a.K = m->F; a.ldw = m->F; a.vec_in = m->gbuf; a.out = m->part_w2;
             prof_mark(m, PC_W2);
-            RLB_TRY(launch_gemv(ctx, m->wdt, PRO_COPY, EPI_F32, a));
+            RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
             RLB_TRY(tp_reduce(m, m->part_w2, d));
         }
     }
@@ -225,7 +236,7 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         a.gain = m->norm; a.eps = m->p.norm_eps;
         a.out = m->tp == 1 ? m->logits : m->logits_local;
         prof_mark(m, PC_HEAD);
-        RLB_TRY(launch_gemv(ctx, RLB_F32, PRO_NORM, EPI_F32, a));
+        RLB_TRY(gemv_decode(m, RLB_F32, PRO_NORM, EPI_F32, a));
         if (m->tp > 1) {
             prof_mark(m, PC_COMM);
             RLB_TRY(nccl_allgather_f32(&m->nccl, m->logits_local, m->logits, (size_t)m->V, ctx->stream));
@@ -340,6 +351,12 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
     return RLB_OK;
 }
 
+// The decode kernels raise scalars[8] when a bounded wait ran out; h points at its host copy.
+int check_device_flag(const int32_t* h) {
+    if (*h != 0) return rlb_fail(RLB_ERR_CUDA, "a decode kernel gave up waiting on a shared-memory barrier (results are invalid)");
+    return RLB_OK;
+}
+
 int check_forward_args(rlb_model* m, rlb_caches* c, const int32_t* tokens, int n, int start_pos) {
     if (!m || !c || !tokens) return rlb_fail(RLB_ERR_INVALID, "forward: null pointer");
     if (!m->finalized) return rlb_fail(RLB_ERR_STATE, "forward: model is not finalized");
@@ -451,6 +468,9 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
         rlb_model_free(m);
         return s;
     }
+    if (const char* e = getenv("RLB_STREAM")) m->use_stream = atoi(e) != 0;
+    if (const char* e = getenv("RLB_PDL")) m->use_pdl = atoi(e) != 0;
+    if (const char* e = getenv("RLB_GRAPH")) m->use_graph = atoi(e) != 0;
     if (ctx->verbose)
         printf("model: dim %d layers %d heads %d (local %d from %d) ffn %d (local %d) vocab %d (local %d) %s tp %d/%d attn split %d\n", p->dim,
                p->n_layers, p->n_heads, m->nh, m->head0, p->ffn_dim, m->F, p->vocab_size, m->V, m->wdt == RLB_F16 ? "f16" : "f32", m->rank, tp,
@@ -681,7 +701,9 @@ int rlb_forward(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32_t n, i
     RLB_CUDA(cudaSetDevice(ctx->device));
     RLB_TRY(forward_common(m, c, tokens, n, start_pos, false));
     RLB_CUDA(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->p.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 9, m->scalars + 8, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    RLB_TRY(check_device_flag(m->h_scalars + 9));
     memcpy(logits_out, m->h_logits, (size_t)m->p.vocab_size * 4);
     return RLB_OK;
 }
@@ -694,7 +716,9 @@ int rlb_forward_greedy(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32
     RLB_CUDA(cudaSetDevice(ctx->device));
     RLB_TRY(forward_common(m, c, tokens, n, start_pos, true));
     RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 8, m->scalars + 3, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 9, m->scalars + 8, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    RLB_TRY(check_device_flag(m->h_scalars + 9));
     *next_token = m->h_scalars[8];
     return RLB_OK;
 }
@@ -722,7 +746,9 @@ int rlb_decode_greedy(rlb_model* m, rlb_caches* c, int32_t first_token, int32_t 
     for (int i = done; i < n_steps; i++) RLB_TRY(run_decode_step(m, c, true, &slot));
     RLB_CUDA(cudaEventRecord(e1, ctx->stream));
     RLB_CUDA(cudaMemcpyAsync(m->h_tokens, m->tokens_out, (size_t)n_steps * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 9, m->scalars + 8, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    RLB_TRY(check_device_flag(m->h_scalars + 9));
     memcpy(tokens_out, m->h_tokens, (size_t)n_steps * sizeof(int32_t));
     if (elapsed_ms) {
         float ms = 0.f;
@@ -736,6 +762,8 @@ int rlb_model_set_option(rlb_model* m, const char* name, int64_t value) {
     if (!m || !name) return rlb_fail(RLB_ERR_INVALID, "rlb_model_set_option: null pointer");
     std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
     if (!strcmp(name, "graph")) { m->use_graph = value != 0; return RLB_OK; }
+    if (!strcmp(name, "stream_gemv")) { m->use_stream = value != 0; return RLB_OK; }
+    if (!strcmp(name, "pdl")) { m->use_pdl = value != 0; return RLB_OK; }
     if (!strcmp(name, "profile")) {
         m->profile = value != 0;
         for (double& v : m->prof_ms) v = 0;
