@@ -100,6 +100,18 @@ int rlb_silu_inplace(rlb_tensor* t);
  * bandwidth-bound GEMV kernel, otherwise the tiled GEMM (tcgen05 for f16).            */
 int rlb_matrix_mul_inplace_transposed(rlb_tensor* dst, const rlb_tensor* src, const rlb_tensor* other);
 
+/* Single-query attention over a position-major KV cache: the per-head part of
+ * Attention::forward at decode (src/transformer.rs:727-781) as a standalone op.
+ *   q       1 x (heads*head_dim) f32, already rotated
+ *   kcache  (heads*max_seq_len) x head_dim, f16 or f32, capacity_cols == head_dim:
+ *   vcache  row (h*max_seq_len + t) holds head h, position t
+ *   out     1 x (heads*head_dim) in the cache dtype (f16 results are rounded once)
+ * Attends to positions 0..pos. n_split > 1 splits the positions of each head over that
+ * many CTAs and combines their partial results (1..64). Scratch for the partial results
+ * is owned by the context and grown on demand.                                        */
+int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
+                         int32_t heads, int32_t max_seq_len, int32_t pos, int32_t n_split);
+
 /* ------------------------------------------------------------------------------------
  * Tier 2: the fused model-level path (what Transformer::forward becomes).
  * ---------------------------------------------------------------------------------- */

@@ -74,6 +74,7 @@ int rlb_ctx_destroy(rlb_ctx* ctx) {
     if (!ctx) return RLB_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->op_scratch) cudaFree(ctx->op_scratch);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RLB_OK;
@@ -283,3 +284,52 @@ int rlb_matrix_mul_inplace_transposed(rlb_tensor* dst, const rlb_tensor* src, co
 }
 
 }  // extern "C"
+
+// Shape checks shared by the attention entry points. Returns the head dimension in *hd_out.
+int attention_check(const rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache, int32_t heads,
+                    int32_t max_seq_len, int32_t pos, int32_t n_split, int* hd_out) {
+    RLB_TRY(same_ctx(out, q));
+    RLB_TRY(same_ctx(out, kcache));
+    RLB_TRY(same_ctx(out, vcache));
+    if (heads < 1 || max_seq_len < 1 || pos < 0 || pos >= max_seq_len || n_split < 1 || n_split > 64)
+        return rlb_fail(RLB_ERR_INVALID, "attention: bad heads %d, max_seq_len %d, pos %d or n_split %d", heads, max_seq_len, pos, n_split);
+    const int64_t hd = kcache->cols;
+    if (kcache->cap != hd || vcache->cap != hd || vcache->cols != hd || kcache->rows != (int64_t)heads * max_seq_len ||
+        vcache->rows != kcache->rows || kcache->dtype != vcache->dtype)
+        return rlb_fail(RLB_ERR_INVALID, "attention: caches must be (heads*max_seq_len) x head_dim without row padding");
+    if (q->dtype != RLB_F32 || q->rows != 1 || q->cols != (int64_t)heads * hd) return rlb_fail(RLB_ERR_INVALID, "attention: q must be 1 x heads*head_dim f32");
+    if (out->dtype != kcache->dtype || out->rows != 1 || out->cols != (int64_t)heads * hd)
+        return rlb_fail(RLB_ERR_INVALID, "attention: out must be 1 x heads*head_dim in the cache dtype");
+    *hd_out = (int)hd;
+    return RLB_OK;
+}
+
+extern "C" int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache, int32_t heads,
+                                    int32_t max_seq_len, int32_t pos, int32_t n_split) {
+    int hd = 0;
+    RLB_TRY(attention_check(out, q, kcache, vcache, heads, max_seq_len, pos, n_split, &hd));
+    OP_PROLOGUE(ctx, out);
+    // scratch: [pos : 256 B][counters : heads, padded to 256 B][records]
+    const size_t cnt_bytes = ((size_t)heads * sizeof(unsigned int) + 255) & ~(size_t)255;
+    const size_t need = 256 + cnt_bytes + attn_decode_scratch_floats(heads, hd, n_split) * sizeof(float);
+    if (need > ctx->op_scratch_bytes) {
+        RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->op_scratch) cudaFree(ctx->op_scratch);
+        ctx->op_scratch = nullptr;
+        ctx->op_scratch_bytes = 0;
+        cudaError_t e = cudaMalloc(&ctx->op_scratch, need);
+        if (e != cudaSuccess) return rlb_fail(RLB_ERR_OOM, "attention scratch (%zu bytes): %s", need, cudaGetErrorString(e));
+        ctx->op_scratch_bytes = need;
+    }
+    char* base = (char*)ctx->op_scratch;
+    RLB_CUDA(cudaMemsetAsync(base, 0, 256 + cnt_bytes, ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(base, &pos, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    AttnDecodeArgs a;
+    a.q = (const float*)q->d; a.kcache = kcache->d; a.vcache = vcache->d; a.out = out->d;
+    a.pos_ptr = (const int32_t*)base; a.heads = heads; a.hd = hd; a.max_seq = max_seq_len; a.n_split = n_split;
+    a.counters = (unsigned int*)(base + 256);
+    a.scratch = (float*)(base + 256 + cnt_bytes);
+    RLB_TRY(launch_attn_decode(ctx, kcache->dtype, a, 0));
+    RLB_CUDA(cudaEventRecord(out->ready, ctx->stream));
+    return RLB_OK;
+}

@@ -42,6 +42,8 @@ struct rlb_ctx {
     cudaStream_t stream = nullptr;
     std::recursive_mutex mu;
     uint64_t launches = 0;  // kernels launched by this library on this context
+    void* op_scratch = nullptr;  // scratch of the standalone attention op, grown on demand
+    size_t op_scratch_bytes = 0;
 };
 
 struct rlb_tensor {

@@ -94,6 +94,10 @@ class CudaTensor:
     def matrix_mul_inplace_transposed(self, src, other):
         check(_ffi.lib().rlb_matrix_mul_inplace_transposed(self._h, src._h, other._h))
 
+    def attention_decode(self, q, kcache, vcache, heads, max_seq_len, pos, n_split=1):
+        """self <- single-query attention of q over positions 0..pos of the caches."""
+        check(_ffi.lib().rlb_attention_decode(self._h, q._h, kcache._h, vcache._h, heads, max_seq_len, pos, n_split))
+
     def free(self):
         if self._h:
             _ffi.lib().rlb_tensor_free(self._h)

@@ -111,3 +111,42 @@ def test_shape_and_dtype_errors(cuda_ctx):
     with pytest.raises(RllamaError):
         a.hadamard_product_inplace(b)
     assert cuda_ctx.kernel_launches() > 0
+
+
+def attention_reference(q, k, v, heads, hd, max_seq, pos):
+    """float64 softmax(q K^T / sqrt(hd)) V per head over positions 0..pos
+    (rllama src/transformer.rs:768-779)."""
+    out = np.zeros(heads * hd)
+    for h in range(heads):
+        K = k[h * max_seq: h * max_seq + pos + 1].astype(np.float64)
+        V = v[h * max_seq: h * max_seq + pos + 1].astype(np.float64)
+        s = K @ q[0, h * hd:(h + 1) * hd].astype(np.float64) / np.sqrt(hd)
+        p = np.exp(s - s.max())
+        out[h * hd:(h + 1) * hd] = (p / p.sum()) @ V
+    return out
+
+
+def attention_case(rng, heads, hd, max_seq, dtype):
+    q = rng.normal(0, 1, (1, heads * hd)).astype(np.float32)
+    k = rng.normal(0, 1, (heads * max_seq, hd)).astype(dtype)
+    v = rng.normal(0, 1, (heads * max_seq, hd)).astype(dtype)
+    return q, k, v
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_attention_decode_op(cuda_ctx, dtype):
+    rng = np.random.default_rng(5)
+    for heads, hd, max_seq, pos, n_split in [(4, 64, 96, 70, 1), (4, 64, 96, 70, 4), (3, 128, 300, 299, 5), (2, 128, 64, 0, 2),
+                                             (8, 128, 2048, 2047, 16)]:
+        q, k, v = attention_case(rng, heads, hd, max_seq, dtype)
+        tq, tk, tv = cuda_ctx.upload(q), cuda_ctx.upload(k), cuda_ctx.upload(v)
+        out = cuda_ctx.zeros(1, heads * hd, F16 if dtype == np.float16 else F32)
+        out.attention_decode(tq, tk, tv, heads, max_seq, pos, n_split)
+        got = out.to_numpy().astype(np.float64)[0]
+        want = attention_reference(q, k, v, heads, hd, max_seq, pos)
+        assert np.abs(got - want).max() <= (2e-3 if dtype == np.float16 else 2e-6), (heads, hd, max_seq, pos, n_split)
+        for t in (tq, tk, tv, out):
+            t.free()
+    with pytest.raises(RllamaError):
+        bad = cuda_ctx.zeros(1, 8, F32)
+        bad.attention_decode(bad, bad, bad, 1, 4, 9, 1)
