@@ -112,6 +112,18 @@ int rlb_matrix_mul_inplace_transposed(rlb_tensor* dst, const rlb_tensor* src, co
 int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
                          int32_t heads, int32_t max_seq_len, int32_t pos, int32_t n_split);
 
+/* rlb_attention_decode without any allocation (no counterpart in the reference). For hosts
+ * that cannot let the library allocate on the token path: a server whose HBM is already
+ * split between weights and KV caches, or a latency-critical thread that must not stall the
+ * device in cudaMalloc / cudaFree. The split-attention scratch is a fixed 1 MiB (+ 1.25 KiB
+ * header) array inside the library, held by every GPU that loads it until the process ends.
+ * Same arguments and results as rlb_attention_decode. Fails with RLB_ERR_LIMIT when
+ * heads > 256 or heads * n_split * (head_dim + 2) > 262144 floats. All calls on one device
+ * share the array: calls that overlap on the GPU race, so serialise them. The first call on
+ * a device resolves the array's device address; make it before any stream capture.      */
+int rlb_attention_decode_static(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
+                                int32_t heads, int32_t max_seq_len, int32_t pos, int32_t n_split);
+
 /* ------------------------------------------------------------------------------------
  * Tier 2: the fused model-level path (what Transformer::forward becomes).
  * ---------------------------------------------------------------------------------- */

@@ -284,3 +284,85 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
     count_launch(ctx);
     return RLB_OK;
 }
+
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the standalone attention op.
+//
+// Some hosts of this library cannot let it allocate device memory while tokens are being
+// generated: an inference server that has already divided all of HBM between weights and KV
+// caches has nothing left for cudaMalloc to hand out, and a worker thread on the token path
+// cannot afford cudaMalloc / cudaFree, which stall every stream of the device while they run.
+// For those callers the split-attention kernel's scratch (per-split partial outputs, the
+// per-head arrival counters and the position word) lives in the fixed array below instead of
+// in memory obtained at call time. Every GPU that loads the library holds the array
+// (kStaticBytes) until the process exits.
+//
+// Limits and rules:
+//  * heads <= kStaticMaxHeads and heads * n_split * (head_dim + 2) floats <= kStaticRecordFloats,
+//    otherwise the call fails with RLB_ERR_LIMIT;
+//  * all calls on a device share the one array and it keeps the last call's contents: the words
+//    that must start at zero are cleared on every call, and two calls that overlap on the GPU
+//    (different streams or contexts of the same device) race on it -- serialise them;
+//  * the first call on each device looks up the array's device address
+//    (cudaGetSymbolAddress); make that first call before any stream capture begins.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticMaxHeads = 256;
+constexpr size_t kStaticHeaderFloats = 64 + kStaticMaxHeads;      // position word (padded) + counters
+constexpr size_t kStaticRecordFloats = 256 * 1024;                // 1 MiB of partial records
+constexpr size_t kStaticFloats = kStaticHeaderFloats + kStaticRecordFloats;
+constexpr size_t kStaticBytes = kStaticFloats * sizeof(float);
+
+// In host code this name is only a handle for the runtime's symbol lookup, never an address a
+// kernel could use; the device address is obtained once per device below.
+static __device__ __align__(256) float g_attn_static[kStaticFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_attn_static_addr[kMaxDevices] = {nullptr};
+std::mutex g_attn_static_mu;
+
+int static_scratch_address(int device, float** out) {
+    if (device < 0 || device >= kMaxDevices) return rlb_fail(RLB_ERR_LIMIT, "attention (static scratch): device index %d is beyond %d", device, kMaxDevices);
+    std::lock_guard<std::mutex> g(g_attn_static_mu);
+    if (!g_attn_static_addr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static);  // the caller made `device` current
+        if (e != cudaSuccess || !p) return rlb_fail(RLB_ERR_CUDA, "cudaGetSymbolAddress(static attention scratch): %s", cudaGetErrorString(e));
+        g_attn_static_addr[device] = static_cast<float*>(p);
+    }
+    *out = g_attn_static_addr[device];
+    return RLB_OK;
+}
+
+}  // namespace
+
+extern "C" int rlb_attention_decode_static(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
+                                           int32_t heads, int32_t max_seq_len, int32_t pos, int32_t n_split) {
+    int hd = 0;
+    RLB_TRY(attention_check(out, q, kcache, vcache, heads, max_seq_len, pos, n_split, &hd));
+    if (heads > kStaticMaxHeads)
+        return rlb_fail(RLB_ERR_LIMIT, "attention (static scratch): %d heads exceed the maximum of %d", heads, kStaticMaxHeads);
+    const size_t need = attn_decode_scratch_floats(heads, hd, n_split);
+    if (need > kStaticRecordFloats)
+        return rlb_fail(RLB_ERR_LIMIT, "attention (static scratch): heads %d x n_split %d x (head_dim %d + 2) = %zu floats exceed the fixed %zu",
+                        heads, n_split, hd, need, kStaticRecordFloats);
+    rlb_ctx* ctx = out->ctx;
+    std::lock_guard<std::recursive_mutex> g(ctx->mu);
+    RLB_CUDA(cudaSetDevice(ctx->device));
+    float* base = nullptr;
+    RLB_TRY(static_scratch_address(ctx->device, &base));
+    // the position word and the arrival counters must start from known values on every call
+    RLB_CUDA(cudaMemsetAsync(base, 0, kStaticHeaderFloats * sizeof(float), ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(base, &pos, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+    AttnDecodeArgs a;
+    a.q = (const float*)q->d; a.kcache = kcache->d; a.vcache = vcache->d; a.out = out->d;
+    a.pos_ptr = reinterpret_cast<const int32_t*>(base);
+    a.heads = heads; a.hd = hd; a.max_seq = max_seq_len; a.n_split = n_split;
+    a.counters = reinterpret_cast<unsigned int*>(base + 64);
+    a.scratch = base + kStaticHeaderFloats;
+    RLB_TRY(launch_attn_decode(ctx, kcache->dtype, a, 0));
+    RLB_CUDA(cudaEventRecord(out->ready, ctx->stream));
+    return RLB_OK;
+}

@@ -134,6 +134,9 @@ struct AttnDecodeArgs {
     unsigned int* counters = nullptr;  // [heads], zero between launches
 };
 int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs& a, int allow_pdl);
+// Argument checks shared by the standalone attention entry points (context.cu).
+int attention_check(const rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache, int32_t heads,
+                    int32_t max_seq_len, int32_t pos, int32_t n_split, int* hd_out);
 size_t attn_decode_scratch_floats(int heads, int hd, int n_split);
 
 struct AttnPrefillArgs {

@@ -98,6 +98,12 @@ class CudaTensor:
         """self <- single-query attention of q over positions 0..pos of the caches."""
         check(_ffi.lib().rlb_attention_decode(self._h, q._h, kcache._h, vcache._h, heads, max_seq_len, pos, n_split))
 
+    def attention_decode_static(self, q, kcache, vcache, heads, max_seq_len, pos, n_split=1):
+        """Same as ``attention_decode`` but allocation-free: the kernel's scratch is a fixed
+        array inside the library (for hosts that cannot allocate on the token path). Fails
+        beyond 256 heads or 262144 scratch floats; calls on one device must not overlap."""
+        check(_ffi.lib().rlb_attention_decode_static(self._h, q._h, kcache._h, vcache._h, heads, max_seq_len, pos, n_split))
+
     def free(self):
         if self._h:
             _ffi.lib().rlb_tensor_free(self._h)
