@@ -14,6 +14,7 @@
 #include "internal.h"
 
 #include <cfloat>
+#include <cstdlib>
 
 namespace {
 
@@ -225,6 +226,164 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefil
     for (int c = threadIdx.x; c < hd; c += kThreads) out[c] = cast_out<CT>(o_sh[c] / l);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode attention, low-latency form for head_dim 64 / 128: one warp per position, online softmax.
+//
+// A warp owns positions t0 + warp, t0 + warp + 8, ...; its 32 lanes split head_dim (DPL = HD / 32
+// values each), so one position's K (or V) row is one coalesced warp load. K and V rows of a
+// batch of PB positions are all requested before any arithmetic: one memory round trip per batch,
+// none of it waiting on the softmax state. The running (max, sum, output) triple is per warp; the
+// eight warps are merged once through shared memory, and the splits of a head are merged by the
+// last CTA to arrive (as in the general kernel above). Only CTAs whose range is not empty take
+// part, and a head with a single live split writes its output directly.
+// ---------------------------------------------------------------------------------------------
+template <typename CT, int DPL> struct RowVec;
+template <> struct RowVec<__half, 4> { typedef uint2 T; };
+template <> struct RowVec<__half, 2> { typedef uint32_t T; };
+template <> struct RowVec<float, 4> { typedef uint4 T; };
+template <> struct RowVec<float, 2> { typedef uint2 T; };
+
+template <typename CT, int DPL> __device__ __forceinline__ void row_unpack(const typename RowVec<CT, DPL>::T& v, float (&f)[DPL]);
+template <> __device__ __forceinline__ void row_unpack<__half, 4>(const uint2& v, float (&f)[4]) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+template <> __device__ __forceinline__ void row_unpack<__half, 2>(const uint32_t& v, float (&f)[2]) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    f[0] = a.x; f[1] = a.y;
+}
+template <> __device__ __forceinline__ void row_unpack<float, 4>(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void row_unpack<float, 2>(const uint2& v, float (&f)[2]) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+}
+
+constexpr int kFastMinChunk = 64;  // positions per CTA at least (a multiple of kWarps)
+
+__host__ __device__ inline int fast_chunk(int T, int ns) {
+    int chunk = (T + ns - 1) / ns;
+    chunk = (chunk + kFastMinChunk - 1) / kFastMinChunk * kFastMinChunk;
+    return chunk;
+}
+
+template <typename CT, int HD>
+__global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDecodeArgs a) {
+    constexpr int DPL = HD / 32;
+    constexpr int PB = 8;  // positions per warp per batch
+    typedef typename RowVec<CT, DPL>::T RV;
+    __shared__ float w_m[kWarps], w_l[kWarps];
+    __shared__ float w_o[kWarps][HD];
+    __shared__ unsigned int ticket_sh;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int head = blockIdx.x, split = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int T = *a.pos_ptr + 1;
+    const int chunk = fast_chunk(T, a.n_split);
+    const int active = (T + chunk - 1) / chunk;  // splits with at least one position
+    if (split >= active) return;
+    const int t0 = split * chunk, t1 = min(T, t0 + chunk);
+    const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * HD + lane * DPL;
+    const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * HD + lane * DPL;
+    float q[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; d++) q[d] = a.q[head * HD + lane * DPL + d];
+    const float scale = 1.0f / sqrtf((float)HD);  // src/transformer.rs:770
+    float m = -FLT_MAX, l = 0.f, acc[DPL];
+#pragma unroll
+    for (int d = 0; d < DPL; d++) acc[d] = 0.f;
+
+    for (int tb = t0 + warp; tb < t1; tb += kWarps * PB) {
+        RV kv[PB], vv[PB];
+#pragma unroll
+        for (int j = 0; j < PB; j++) {
+            const int t = tb + j * kWarps;
+            if (t < t1) {
+                kv[j] = *reinterpret_cast<const RV*>(kbase + (int64_t)t * HD);
+                vv[j] = *reinterpret_cast<const RV*>(vbase + (int64_t)t * HD);
+            }
+        }
+        float sc[PB];
+#pragma unroll
+        for (int j = 0; j < PB; j++) {
+            float dot = 0.f;
+            if (tb + j * kWarps < t1) {
+                float kf[DPL];
+                row_unpack<CT, DPL>(kv[j], kf);
+#pragma unroll
+                for (int d = 0; d < DPL; d++) dot = fmaf(q[d], kf[d], dot);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            sc[j] = (tb + j * kWarps < t1) ? dot * scale : -FLT_MAX;
+        }
+        float bm = sc[0];
+#pragma unroll
+        for (int j = 1; j < PB; j++) bm = fmaxf(bm, sc[j]);
+        const float m_new = fmaxf(m, bm);
+        const float rescale = expf(m - m_new);  // first batch: exp(-huge) = 0 against zero state
+        l *= rescale;
+#pragma unroll
+        for (int d = 0; d < DPL; d++) acc[d] *= rescale;
+#pragma unroll
+        for (int j = 0; j < PB; j++) {
+            if (tb + j * kWarps < t1) {
+                const float p = expf(sc[j] - m_new);
+                l += p;
+                float vf[DPL];
+                row_unpack<CT, DPL>(vv[j], vf);
+#pragma unroll
+                for (int d = 0; d < DPL; d++) acc[d] = fmaf(p, vf[d], acc[d]);
+            }
+        }
+        m = m_new;
+    }
+    // merge the eight warps
+    if (lane == 0) { w_m[warp] = m; w_l[warp] = l; }
+#pragma unroll
+    for (int d = 0; d < DPL; d++) w_o[warp][lane * DPL + d] = acc[d];
+    __syncthreads();
+    float M = w_m[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; w++) M = fmaxf(M, w_m[w]);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) L += w_l[w] * expf(w_m[w] - M);
+    CT* out = reinterpret_cast<CT*>(a.out) + head * HD;
+    float o = 0.f;
+    const int c = threadIdx.x;
+    if (c < HD) {
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) o += w_o[w][c] * expf(w_m[w] - M);
+    }
+    if (active == 1) {
+        if (c < HD) out[c] = cast_out<CT>(o / L);
+        return;
+    }
+    float* rec = a.scratch + ((int64_t)head * a.n_split + split) * (HD + 2);
+    if (c < HD) rec[c] = o;
+    if (c == 0) { rec[HD] = M; rec[HD + 1] = L; }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_sh = atomicAdd(a.counters + head, 1u);
+    __syncthreads();
+    if (ticket_sh != (unsigned)(active - 1)) return;
+    __threadfence();
+    const float* recs = a.scratch + (int64_t)head * a.n_split * (HD + 2);
+    float GM = -FLT_MAX;
+    for (int s = 0; s < active; s++) GM = fmaxf(GM, __ldcg(recs + s * (HD + 2) + HD));
+    float GL = 0.f;
+    for (int s = 0; s < active; s++) GL += __ldcg(recs + s * (HD + 2) + HD + 1) * expf(__ldcg(recs + s * (HD + 2) + HD) - GM);
+    if (c < HD) {
+        float go = 0.f;
+        for (int s = 0; s < active; s++) go += __ldcg(recs + s * (HD + 2) + c) * expf(__ldcg(recs + s * (HD + 2) + HD) - GM);
+        out[c] = cast_out<CT>(go / GL);
+    }
+    if (threadIdx.x == 0) a.counters[head] = 0;  // ready for the next launch
+}
+
 size_t attn_smem_bytes(int hd, int vec, int max_positions) {
     return sizeof(float) * ((size_t)2 * hd + (size_t)kThreads * vec + (size_t)max_positions);
 }
@@ -251,7 +410,17 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = allow_pdl ? 1 : 0;
-    if (cache_dtype == RLB_F16) {
+    static const bool use_fast = getenv("RLB_ATTN_FAST") == nullptr || atoi(getenv("RLB_ATTN_FAST")) != 0;
+    if (use_fast && (a.hd == 64 || a.hd == 128)) {
+        lc.dynamicSmemBytes = 0;
+        if (cache_dtype == RLB_F16) {
+            if (a.hd == 128) RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<__half, 128>, a));
+            else RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<__half, 64>, a));
+        } else {
+            if (a.hd == 128) RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<float, 128>, a));
+            else RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<float, 64>, a));
+        }
+    } else if (cache_dtype == RLB_F16) {
         static bool set = false;
         if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
         RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_kernel<__half>, a));

@@ -1,0 +1,90 @@
+"""Tensor parallelism on real GPUs (needs two): two processes, one per GPU, shard the model
+through the C ABI, exchange over NCCL and must reproduce the CPU oracle's logits within the
+single-GPU bounds; both ranks must return identical logits."""
+import os
+import sys
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _device_count():
+    import ctypes
+    from rllama_b200 import _ffi
+    n = ctypes.c_int(0)
+    _ffi.lib().rlb_device_count(ctypes.byref(n))
+    return n.value
+
+
+def _worker(rank, world, tmpdir, f16, heads):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from rllama_b200 import Cuda, DataSettings, Transformer
+    from rllama_b200 import synthetic as S
+    from helpers import cfg_variant
+
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, n_heads=heads, dim=64 * heads, max_seq_len=32)
+    cl = Cuda(nth_device=rank)
+    ds = DataSettings(cl=cl)
+    if f16:
+        ds = ds.force_f16()
+    m = Transformer(cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"], cfg["max_seq_len"], cfg["norm_eps"], ds,
+                    tp_rank=rank, tp_size=world)
+    id_path = os.path.join(tmpdir, "nccl_id.bin")
+    if rank == 0:
+        uid = Transformer.nccl_unique_id()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.rename(id_path + ".tmp", id_path)
+    else:
+        for _ in range(600):
+            if os.path.exists(id_path):
+                break
+            time.sleep(0.05)
+        uid = open(id_path, "rb").read()
+    m.nccl_init(uid)
+    S.load_into(m, cfg)
+    m.finalize()
+    prompt = S.synth_tokens(7, cfg["vocab"])
+    c = m.make_caches()
+    outs = [m.forward(prompt, 0, c)]
+    toks = np.load(os.path.join(tmpdir, "oracle_tokens.npy"))
+    for i, t in enumerate(toks):
+        outs.append(m.forward([int(t)], 7 + i, c))
+    first = m.forward_greedy(prompt, 0, m.make_caches())
+    np.save(os.path.join(tmpdir, "logits_rank%d.npy" % rank), np.stack(outs))
+    np.save(os.path.join(tmpdir, "first_rank%d.npy" % rank), np.array([first]))
+    cl.flush()
+
+
+@pytest.mark.parametrize("f16,heads", [(False, 4), (True, 4), (True, 3)])
+def test_tp2_matches_oracle(tmp_path, f16, heads):
+    if _device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from rllama_b200 import synthetic as S
+    from helpers import build_pair, cfg_variant
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, n_heads=heads, dim=64 * heads, max_seq_len=32)
+    _, orc = build_pair(cfg, f16, with_gpu=False)
+    prompt = S.synth_tokens(7, cfg["vocab"])
+    oc = orc.make_caches()
+    want = [orc.forward(prompt, 0, oc)]
+    toks = []
+    for i in range(4):
+        toks.append(int(np.argmax(want[-1])))
+        want.append(orc.forward([toks[-1]], 7 + i, oc))
+    np.save(str(tmp_path / "oracle_tokens.npy"), np.array(toks, dtype=np.int32))
+    mp.spawn(_worker, args=(2, str(tmp_path), f16, heads), nprocs=2, join=True)
+    r0 = np.load(str(tmp_path / "logits_rank0.npy")); r1 = np.load(str(tmp_path / "logits_rank1.npy"))
+    assert np.array_equal(r0, r1)  # every rank holds the same logits, bit for bit
+    want = np.stack(want)
+    if f16:
+        assert float(np.abs(r0 - want).max()) <= 2e-2
+    else:
+        assert float(np.abs(r0 - want).max() / np.abs(want).max()) <= 1e-4
+    assert int(np.load(str(tmp_path / "first_rank0.npy"))[0]) == int(np.load(str(tmp_path / "first_rank1.npy"))[0])
