@@ -242,6 +242,12 @@ def main():
         ids = [Transformer.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         model.nccl_init(ids[0])
+        tp_mode = os.environ.get("RLB_TP_MODE", "push")
+        if tp_mode == "push":
+            handles = [None] * world
+            dist.all_gather_object(handles, model.peer_export())
+            model.peer_import(handles)
+            model.set_tp_mode("push")
 
     prompt = S.synth_tokens(P, cfg["vocab"])
 
@@ -325,7 +331,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": ms_per_token, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16" if cfg["f16"] else "f32", "data": "synthetic",
-            "config": {"workload": workload_name(cfg), "parallelism": "tp%d" % world, "context_start": P + Wm, "context_end": P + Wm + K,
+            "config": {"workload": workload_name(cfg), "parallelism": "tp%d" % world, "exchange": (os.environ.get("RLB_TP_MODE", "push") if world > 1 else "none"), "context_start": P + Wm, "context_end": P + Wm + K,
                        "l2": "inputs larger than L2 (every step streams all weights)", "prefill_ms": prefill_ms,
                        "first_tokens": [int(first)] + [int(t) for t in tokens[:4]]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

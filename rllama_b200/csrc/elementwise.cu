@@ -82,13 +82,13 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
 // Greedy choice = TokenSampler with top_k 1 (src/token_sampler.rs:20-28, :127-147): the
 // largest logit; among equal maxima the lowest id (the reference's unstable sort leaves ties
 // unspecified). NaNs sort last, as in the reference's comparator.
-__device__ __forceinline__ void argmax_block(const float* __restrict__ logits, int n, float& best_v, int& best_i) {
+__device__ __forceinline__ void argmax_block(const float* logits, int n, float& best_v, int& best_i) {
     __shared__ float sv[32];
     __shared__ int si[32];
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = logits[i];
+        const float v = __ldcg(logits + i);
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
 #pragma unroll
@@ -106,17 +106,42 @@ __device__ __forceinline__ void argmax_block(const float* __restrict__ logits, i
     best_v = bv; best_i = bi;
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int n, int32_t* __restrict__ out_tok) {
-    float bv; int bi;
-    argmax_block(logits, n, bv, bi);
-    if (threadIdx.x == 0) *out_tok = bi;
+// Tensor-parallel push mode: the logits are written into this GPU's memory by every rank's head
+// kernel; wait (bounded) until all of them have counted themselves in for this step.
+__device__ __forceinline__ void step_wait(const StepSync& sy) {
+    if (sy.wait_flag != nullptr) {
+        if (threadIdx.x == 0) {
+            const unsigned long long target = (unsigned long long)(*sy.epoch) * sy.wait_per_epoch;
+            bool ok = false;
+            for (unsigned int i = 0; i < (1u << 22); i++) {
+                unsigned long long v;
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(sy.wait_flag) : "memory");
+                if (v >= target) { ok = true; break; }
+            }
+            if (!ok) atomicExch(sy.err, 2);
+        }
+        __syncthreads();
+    }
 }
 
-__global__ void argmax_advance_kernel(const float* __restrict__ logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
-                                      int32_t* tokens_out, int32_t cap) {
+// logits may have been written by other GPUs: read them through L2
+__global__ void argmax_kernel(const float* logits, int n, int32_t* __restrict__ out_tok, const StepSync sy) {
+    step_wait(sy);
     float bv; int bi;
     argmax_block(logits, n, bv, bi);
     if (threadIdx.x == 0) {
+        *out_tok = bi;
+        if (sy.epoch) *sy.epoch = *sy.epoch + 1;
+    }
+}
+
+__global__ void argmax_advance_kernel(const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
+                                      int32_t* tokens_out, int32_t cap, const StepSync sy) {
+    step_wait(sy);
+    float bv; int bi;
+    argmax_block(logits, n, bv, bi);
+    if (threadIdx.x == 0) {
+        if (sy.epoch) *sy.epoch = *sy.epoch + 1;
         *tok = bi;
         *pos = *pos + 1;
         const int s = *step;
@@ -246,16 +271,16 @@ int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int r
     return RLB_OK;
 }
 
-int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok) {
-    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, out_tok);
+int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok, const StepSync& sync) {
+    argmax_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, out_tok, sync);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
 }
 
 int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step, int32_t* tokens_out,
-                          int32_t tokens_cap) {
-    argmax_advance_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, tok, pos, step, tokens_out, tokens_cap);
+                          int32_t tokens_cap, const StepSync& sync) {
+    argmax_advance_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, tok, pos, step, tokens_out, tokens_cap, sync);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;

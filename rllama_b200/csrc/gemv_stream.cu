@@ -262,15 +262,31 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         uint4* dst = reinterpret_cast<uint4*>(act);
         for (int i = tid; i < K / VEC; i += kConsumers) dst[i] = src[i];
     } else {
+        if (a.wait_flag != nullptr) {
+            // tensor-parallel push mode: every rank's projection kernel stores its partial sums
+            // into this GPU's inbox and then counts its CTAs in; wait (bounded) for all of them
+            if (tid == 0) {
+                const unsigned long long target = (unsigned long long)(*a.epoch_ptr) * a.wait_per_epoch;
+                bool ok = false;
+                for (uint32_t i = 0; i < (1u << 22) && !*dead; i++) {
+                    unsigned long long v;
+                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(a.wait_flag) : "memory");
+                    if (v >= target) { ok = true; break; }
+                }
+                if (!ok) { *dead = 1; atomicExch(cfg.err, 2); }
+            }
+            consumer_sync();
+        }
         const float* xin = a.x_in;
         if (a.tok_ptr) xin += (int64_t)(*a.tok_ptr) * K;
         float ss = 0.f;
         for (int i = tid * 4; i < K; i += kConsumers * 4) {
             float4 v = *reinterpret_cast<const float4*>(xin + i);
             if (a.n_parts > 0) {
-                float4 sacc = *reinterpret_cast<const float4*>(a.parts + i);
+                // the partial sums may come from other GPUs: read them through L2
+                float4 sacc = __ldcg(reinterpret_cast<const float4*>(a.parts + i));
                 for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
-                    const float4 t = *reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i);
+                    const float4 t = __ldcg(reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i));
                     sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
                 }
                 if (a.round_parts) {
@@ -393,34 +409,43 @@ int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     return RLB_OK;
 }
 
-template <typename WT, int PRO, int EPI>
-int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
+// Rows per tile and vectors per lane for a shape; rb == 0 means "not handled here".
+struct ShapeCfg { int rb; int j; };
+ShapeCfg pick_cfg(int epilogue, const GemvArgs& a) {
     load_tuning();
-    constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
-    const int unit = (EPI == EPI_QKV) ? a.nq : a.rows;
-    // stage = NMAT * RB * J * 4 KB
-    const int J = g_st.j2 ? 2 : 1;
-    int RB = g_st.rb > 0 ? g_st.rb / NMAT : g_st.stage_kb / 4 / NMAT / J;
+    const int nmat = (epilogue == EPI_SWIGLU) ? 2 : 1;
+    const int unit = (epilogue == EPI_QKV) ? a.nq : a.rows;
+    const int J = g_st.j2 ? 2 : 1;  // stage = nmat * RB * J * 4 KB
+    int RB = g_st.rb > 0 ? g_st.rb / nmat : g_st.stage_kb / 4 / nmat / J;
     if (RB > 8) RB = 8;
     if (RB < 1) RB = 1;
     while (RB > 1 && (unit % RB != 0 || a.rows % RB != 0)) RB >>= 1;
-    if (EPI == EPI_QKV && RB < 2) return rlb_fail(RLB_ERR_INVALID, "gemv: q/k/v projection needs an even number of rows per head");
-    if (J == 1) {
-        switch (RB) {
+    if (RB < 2) return ShapeCfg{0, J};
+    if (nmat == 2 && RB > 4) RB = 4;
+    return ShapeCfg{RB, J};
+}
+
+template <typename WT, int PRO, int EPI>
+int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
+    constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
+    const ShapeCfg sc = pick_cfg(EPI, a);
+    if (sc.rb == 0) return RLB_ERR_STATE;  // caller falls back to the register-staged kernel
+    if (sc.j == 1) {
+        switch (sc.rb) {
             case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI>(ctx, a, err_flag, pdl);
             case 4: return launch_cfg<WT, 4, 1, PRO, EPI>(ctx, a, err_flag, pdl);
             case 2: return launch_cfg<WT, 2, 1, PRO, EPI>(ctx, a, err_flag, pdl);
             default: break;
         }
     } else {
-        switch (RB) {
+        switch (sc.rb) {
             case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 2, PRO, EPI>(ctx, a, err_flag, pdl);
             case 4: return launch_cfg<WT, 4, 2, PRO, EPI>(ctx, a, err_flag, pdl);
             case 2: return launch_cfg<WT, 2, 2, PRO, EPI>(ctx, a, err_flag, pdl);
             default: break;
         }
     }
-    return RLB_ERR_STATE;  // caller falls back to the register-staged kernel
+    return RLB_ERR_STATE;
 }
 
 template <typename WT>
@@ -434,13 +459,26 @@ int launch_typed(rlb_ctx* ctx, int prologue, int epilogue, const GemvArgs& a, in
 
 }  // namespace
 
+static bool stream_shape_ok(rlb_dtype dtype, int prologue, const GemvArgs& a) {
+    const int vec = dtype == RLB_F16 ? 8 : 4;
+    if (a.K <= 0 || a.rows < 2 || a.K % vec != 0 || a.ldw % vec != 0 || (prologue == PRO_NORM && a.K % 4 != 0)) return false;
+    if ((a.ldw * (int64_t)(dtype == RLB_F16 ? 2 : 4)) % 16 != 0) return false;  // bulk copies need 16-byte aligned rows
+    return true;
+}
+
+int gemv_stream_grid(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a) {
+    if (!stream_shape_ok(dtype, prologue, a)) return 0;
+    const ShapeCfg sc = pick_cfg(epilogue, a);
+    if (sc.rb == 0) return 0;
+    const int n_tiles = a.rows / sc.rb;
+    return n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
+}
+
 // Returns RLB_ERR_STATE (without recording an error message) when the shape is not handled
 // here, so that the caller can use the register-staged kernel instead.
 int launch_gemv_stream(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a, int* err_flag, int allow_pdl) {
     load_tuning();
-    const int vec = dtype == RLB_F16 ? 8 : 4;
-    if (a.K <= 0 || a.rows < 2 || a.K % vec != 0 || a.ldw % vec != 0 || (prologue == PRO_NORM && a.K % 4 != 0)) return RLB_ERR_STATE;
-    if ((a.ldw * (int64_t)(dtype == RLB_F16 ? 2 : 4)) % 16 != 0) return RLB_ERR_STATE;  // bulk copies need 16-byte aligned rows
+    if (!stream_shape_ok(dtype, prologue, a)) return RLB_ERR_STATE;
     const bool pdl = allow_pdl && g_st.pdl;
     return dtype == RLB_F16 ? launch_typed<__half>(ctx, prologue, epilogue, a, err_flag, pdl)
                             : launch_typed<float>(ctx, prologue, epilogue, a, err_flag, pdl);

@@ -102,6 +102,10 @@ struct GemvArgs {
     int n_outs = 0;                  // 0: write `out` only
     int64_t out_offset = 0;          // added to row for pushed writes
     unsigned long long* flags[RLB_MAX_TP] = {nullptr};  // per-destination arrival counters (push mode)
+    // PRO_NORM in push mode: before reading `parts`, wait until *wait_flag >= *epoch_ptr * wait_per_epoch
+    const unsigned long long* wait_flag = nullptr;
+    unsigned long long wait_per_epoch = 0;
+    const int32_t* epoch_ptr = nullptr;
     // EPI_QKV
     float* qbuf = nullptr;
     void* kcache = nullptr;          // this layer's K cache [heads][max_seq][hd]
@@ -116,6 +120,8 @@ int launch_gemv(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const
 // Bulk-copy staged variant (gemv_stream.cu). Returns RLB_ERR_STATE, without an error message,
 // for shapes it does not handle. err_flag: device int raised when a bounded wait ran out.
 int launch_gemv_stream(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& args, int* err_flag, int allow_pdl);
+// Grid size launch_gemv_stream would use for these arguments (0 if it does not take the shape).
+int gemv_stream_grid(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& args);
 // Tuning knobs (read once from the environment by gemv.cu): rows per warp, CTAs per SM.
 void gemv_set_tuning(int rows_per_warp, int ctas_per_sm, int threads);
 
@@ -162,10 +168,18 @@ int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, i
 int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t count, rlb_dtype out_dtype, void* out);
 // x[i] += round_f16?(y[i])
 int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int round_f16);
-int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok);
+// Optional wait of the arg-max kernels for pushed logits (tensor-parallel push mode), and the
+// per-step epoch counter they advance.
+struct StepSync {
+    const unsigned long long* wait_flag = nullptr;  // wait until *wait_flag >= *epoch * wait_per_epoch
+    unsigned long long wait_per_epoch = 0;
+    int32_t* epoch = nullptr;                       // incremented once per decode step (if set)
+    int32_t* err = nullptr;                         // raised when the wait runs out
+};
+int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok, const StepSync& sync = StepSync());
 // greedy feedback: tok <- argmax, pos <- pos + 1, tokens_out[step] <- tok, step <- step + 1
 int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
-                          int32_t* tokens_out, int32_t tokens_cap);
+                          int32_t* tokens_out, int32_t tokens_cap, const StepSync& sync = StepSync());
 int launch_convert(rlb_ctx* ctx, const void* src, rlb_dtype src_dtype, int64_t src_ld, void* dst, rlb_dtype dst_dtype,
                    int64_t dst_ld, int64_t rows, int64_t cols);
 int launch_silu(rlb_ctx* ctx, void* t, rlb_dtype dtype, int64_t rows, int64_t cols, int64_t cap);

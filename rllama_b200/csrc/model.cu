@@ -95,7 +95,14 @@ struct rlb_model {
 
     // tensor parallel
     TpNccl nccl;
-    int tp_mode = 0;
+    int tp_mode = 0;                 // 0: NCCL collectives, 1: fused one-shot push over peer memory
+    // push mode: one exchange buffer per rank, mapped into every peer
+    //   [inbox_wo : tp*dim f32][inbox_w2 : tp*dim f32][logits : vocab f32][flags : (2*L+1) x 16 u64]
+    char* xbuf = nullptr;
+    size_t xbuf_bytes = 0;
+    char* peer_xbuf[RLB_MAX_TP] = {nullptr};  // peer_xbuf[rank] == xbuf
+    bool peers_open = false;
+    uint64_t graph_gen = 0;          // bumped when captured graphs become stale
 
     // options / statistics
     bool use_graph = true;
@@ -116,6 +123,7 @@ struct rlb_caches {
     size_t layer_elems = 0;
     cudaGraphExec_t graph = nullptr;      // decode step that leaves the arg-max in scalars[3]
     cudaGraphExec_t graph_adv = nullptr;  // decode step with on-device token feedback
+    uint64_t graph_gen = 0;               // model->graph_gen the graphs were captured under
     bool warmed = false;
 };
 
@@ -160,9 +168,18 @@ void prof_collect(rlb_model* m) {
     m->prof_steps++;
 }
 
+// Exchange-buffer layout (push mode).
+size_t xb_inbox_wo(const rlb_model*) { return 0; }
+size_t xb_inbox_w2(const rlb_model* m) { return (size_t)m->tp * m->p.dim * 4; }
+size_t xb_logits(const rlb_model* m) { return 2 * (size_t)m->tp * m->p.dim * 4; }
+size_t xb_flags(const rlb_model* m) { return (xb_logits(m) + (size_t)m->p.vocab_size * 4 + 255) & ~(size_t)255; }
+size_t xb_flag(const rlb_model* m, int index) { return xb_flags(m) + (size_t)index * 128; }  // one 128-byte line each
+size_t xb_total(const rlb_model* m) { return xb_flag(m, 2 * m->p.n_layers + 1); }
+bool push_mode(const rlb_model* m) { return m->tp > 1 && m->tp_mode == 1; }
+
 // All-reduce of the partial sums of one projection when the NCCL mode is active.
-int tp_reduce(rlb_model* m, float* part, size_t count) {
-    if (m->tp == 1) return RLB_OK;
+int tp_reduce(rlb_model* m, float* part, size_t count, bool decode = true) {
+    if (m->tp == 1 || (decode && push_mode(m))) return RLB_OK;
     prof_mark(m, PC_COMM);
     return nccl_allreduce_f32(&m->nccl, part, count, m->ctx->stream);
 }
@@ -183,6 +200,30 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     const int32_t* tok = m->scalars + 0;
     const int32_t* pos = m->scalars + 1;
     const bool f16 = m->wdt == RLB_F16;
+    const bool push = push_mode(m);
+    const int n_parts = push ? m->tp : 1;
+    // partial sums: local buffers, or (push mode) the inboxes every rank stores into
+    const float* parts_wo = push ? (const float*)(m->xbuf + xb_inbox_wo(m)) : m->part_wo;
+    const float* parts_w2 = push ? (const float*)(m->xbuf + xb_inbox_w2(m)) : m->part_w2;
+    float* logits = push ? (float*)(m->xbuf + xb_logits(m)) : m->logits;
+
+    // Producer side of an exchange step: store into every rank's inbox, count CTAs in at `flag_index`.
+    auto push_out = [&](GemvArgs& a, size_t inbox_off, int64_t offset, int flag_index) {
+        a.n_outs = m->tp;
+        a.out_offset = offset;
+        for (int r = 0; r < m->tp; r++) {
+            a.outs[r] = (float*)(m->peer_xbuf[r] + inbox_off);
+            a.flags[r] = (unsigned long long*)(m->peer_xbuf[r] + xb_flag(m, flag_index));
+        }
+    };
+    // Consumer side: wait until all tp * grid producer CTAs of this step have counted in.
+    auto push_wait = [&](GemvArgs& a, int flag_index, int producer_grid) {
+        a.wait_flag = (const unsigned long long*)(m->xbuf + xb_flag(m, flag_index));
+        a.wait_per_epoch = (unsigned long long)m->tp * (unsigned long long)producer_grid;
+        a.epoch_ptr = m->scalars + 4;
+    };
+    int grid_wo = 0, grid_w2 = 0, grid_head = 0;
+
     for (int l = 0; l < m->p.n_layers; l++) {
         const LayerW& W = m->L[l];
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
@@ -191,7 +232,10 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             GemvArgs a;
             a.W = W.wqkv; a.rows = 3 * m->nq; a.K = d; a.ldw = d;
             if (l == 0) { a.x_in = m->tok_emb; a.tok_ptr = tok; }
-            else { a.x_in = m->xb; a.parts = m->part_w2; a.n_parts = 1; a.part_stride = d; a.round_parts = f16; }
+            else {
+                a.x_in = m->xb; a.parts = parts_w2; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
+                if (push) push_wait(a, 2 * (l - 1) + 1, grid_w2);
+            }
             a.x_out = m->xa; a.gain = W.attn_norm; a.eps = m->p.norm_eps;
             a.qbuf = m->qbuf; a.kcache = kc; a.vcache = vc; a.rope = m->rope; a.pos_ptr = pos;
             a.nq = m->nq; a.hd = m->hd; a.max_seq = m->p.max_seq_len;
@@ -209,6 +253,11 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         {   // 3. wo
             GemvArgs a;
             a.W = W.wo; a.rows = d; a.K = m->nq; a.ldw = m->nq; a.vec_in = m->obuf; a.out = m->part_wo;
+            if (push) {
+                push_out(a, xb_inbox_wo(m), (int64_t)m->rank * d, 2 * l);
+                grid_wo = gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a);
+                if (grid_wo == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the wo projection");
+            }
             prof_mark(m, PC_WO);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
             RLB_TRY(tp_reduce(m, m->part_wo, d));
@@ -216,7 +265,8 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         {   // 4. residual + norm + w1/w3 + SiLU gate
             GemvArgs a;
             a.W = W.w1; a.W2 = W.w3; a.rows = m->F; a.K = d; a.ldw = d;
-            a.x_in = m->xa; a.parts = m->part_wo; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
+            a.x_in = m->xa; a.parts = parts_wo; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
+            if (push) push_wait(a, 2 * l, grid_wo);
             a.x_out = m->xb; a.gain = W.ffn_norm; a.eps = m->p.norm_eps; a.out = m->gbuf;
             prof_mark(m, PC_W13);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_SWIGLU, a));
@@ -224,6 +274,11 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         {   // 5. w2
             GemvArgs a;
             a.W = W.w2; a.rows = d; a.K = m->F; a.ldw = m->F; a.vec_in = m->gbuf; a.out = m->part_w2;
+            if (push) {
+                push_out(a, xb_inbox_w2(m), (int64_t)m->rank * d, 2 * l + 1);
+                grid_w2 = gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a);
+                if (grid_w2 == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the w2 projection");
+            }
             prof_mark(m, PC_W2);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
             RLB_TRY(tp_reduce(m, m->part_w2, d));
@@ -232,22 +287,35 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     {   // final norm + f32 head (src/transformer.rs:378-381)
         GemvArgs a;
         a.W = m->output; a.rows = m->V; a.K = d; a.ldw = d;
-        a.x_in = m->xb; a.parts = m->part_w2; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
+        a.x_in = m->xb; a.parts = parts_w2; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
+        if (push) push_wait(a, 2 * (m->p.n_layers - 1) + 1, grid_w2);
         a.gain = m->norm; a.eps = m->p.norm_eps;
         a.out = m->tp == 1 ? m->logits : m->logits_local;
+        if (push) {
+            push_out(a, xb_logits(m), (int64_t)m->v0, 2 * m->p.n_layers);
+            grid_head = gemv_stream_grid(ctx, RLB_F32, PRO_NORM, EPI_F32, a);
+            if (grid_head == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the output head");
+        }
         prof_mark(m, PC_HEAD);
         RLB_TRY(gemv_decode(m, RLB_F32, PRO_NORM, EPI_F32, a));
-        if (m->tp > 1) {
+        if (m->tp > 1 && !push) {
             prof_mark(m, PC_COMM);
             RLB_TRY(nccl_allgather_f32(&m->nccl, m->logits_local, m->logits, (size_t)m->V, ctx->stream));
         }
     }
+    StepSync sy;
+    sy.err = m->scalars + 8;
+    if (push) {
+        sy.epoch = m->scalars + 4;  // counts the decode steps run in push mode (starts at 1)
+        sy.wait_flag = (const unsigned long long*)(m->xbuf + xb_flag(m, 2 * m->p.n_layers));
+        sy.wait_per_epoch = (unsigned long long)m->tp * (unsigned long long)grid_head;
+    }
     prof_mark(m, PC_ARGMAX);
     if (advance)
-        RLB_TRY(launch_argmax_advance(ctx, m->logits, m->p.vocab_size, m->scalars + 0, m->scalars + 1, m->scalars + 2, m->tokens_out,
-                                      m->tokens_cap));
+        RLB_TRY(launch_argmax_advance(ctx, logits, m->p.vocab_size, m->scalars + 0, m->scalars + 1, m->scalars + 2, m->tokens_out,
+                                      m->tokens_cap, sy));
     else
-        RLB_TRY(launch_argmax(ctx, m->logits, m->p.vocab_size, m->scalars + 3));
+        RLB_TRY(launch_argmax(ctx, logits, m->p.vocab_size, m->scalars + 3, sy));
     prof_mark(m, -1);
     return RLB_OK;
 }
@@ -263,6 +331,12 @@ int run_decode_step(rlb_model* m, rlb_caches* c, bool advance, cudaGraphExec_t* 
         c->warmed = true;
         if (m->profile) prof_collect(m);
         return RLB_OK;
+    }
+    if (c->graph_gen != m->graph_gen) {  // the exchange mode changed since these graphs were captured
+        if (c->graph) cudaGraphExecDestroy(c->graph);
+        if (c->graph_adv) cudaGraphExecDestroy(c->graph_adv);
+        c->graph = c->graph_adv = nullptr;
+        c->graph_gen = m->graph_gen;
     }
     if (!*slot) {
         const uint64_t before = ctx->launches;
@@ -331,14 +405,14 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len;
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj));
-        RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d));
+        RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, F, n, F, d, f16));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w3, d, m->pf_g3, F, n, F, d, f16));
         RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g3, (int64_t)n * F, m->wdt, m->pf_g));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj));
-        RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d));
+        RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
     }
     // only the last row gets logits (src/transformer.rs:378-381)
@@ -353,6 +427,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
 
 // The decode kernels raise scalars[8] when a bounded wait ran out; h points at its host copy.
 int check_device_flag(const int32_t* h) {
+    if (*h == 2) return rlb_fail(RLB_ERR_COMM, "a decode kernel gave up waiting for another rank's partial sums (results are invalid)");
     if (*h != 0) return rlb_fail(RLB_ERR_CUDA, "a decode kernel gave up waiting on a shared-memory barrier (results are invalid)");
     return RLB_OK;
 }
@@ -462,6 +537,10 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
         if (e == cudaSuccess) e = cudaMallocHost((void**)&m->h_tokens, (size_t)m->tokens_cap * sizeof(int32_t));
         if (e == cudaSuccess) e = cudaMemsetAsync(m->attn_counters, 0, (size_t)m->nh * sizeof(unsigned int), ctx->stream);
         if (e == cudaSuccess) e = cudaMemsetAsync(m->scalars, 0, 16 * sizeof(int32_t), ctx->stream);
+        if (e == cudaSuccess) {  // scalars[4]: decode-step epoch, starts at 1
+            m->h_scalars[4] = 1;
+            e = cudaMemcpyAsync(m->scalars + 4, m->h_scalars + 4, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream);
+        }
         if (e != cudaSuccess) s = rlb_fail(RLB_ERR_CUDA, "model buffers: %s", cudaGetErrorString(e));
     }
     if (s != RLB_OK) {
@@ -569,6 +648,9 @@ int rlb_model_free(rlb_model* m) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     nccl_destroy(&m->nccl);
+    for (int r = 0; r < m->tp; r++)
+        if (m->peers_open && r != m->rank && m->peer_xbuf[r]) cudaIpcCloseMemHandle(m->peer_xbuf[r]);
+    if (m->xbuf) cudaFree(m->xbuf);
     void* ptrs[] = {m->tok_emb, m->norm, m->output, m->rope, m->xa, m->xb, m->qbuf, m->obuf, m->gbuf, m->part_wo, m->part_w2,
                     m->logits_local, m->logits, m->scalars, m->tokens_out, m->attn_scratch, m->attn_counters, m->pf_tokens, m->pf_x,
                     m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g3, m->pf_g, m->pf_last};
@@ -598,12 +680,52 @@ int rlb_tp_nccl_init(rlb_model* m, const void* id128) {
     return nccl_init(&m->nccl, id128, m->rank, m->tp);
 }
 
-int rlb_tp_peer_export(rlb_model*, void*) { return rlb_fail(RLB_ERR_STATE, "peer-memory exchange is not available in this build"); }
-int rlb_tp_peer_import(rlb_model*, const void*, int32_t) { return rlb_fail(RLB_ERR_STATE, "peer-memory exchange is not available in this build"); }
+int rlb_tp_peer_export(rlb_model* m, void* handle128) {
+    if (!m || !handle128) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_export: null pointer");
+    std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
+    RLB_CUDA(cudaSetDevice(m->ctx->device));
+    if (m->tp == 1) return rlb_fail(RLB_ERR_STATE, "rlb_tp_peer_export: the model is not tensor parallel");
+    if (!m->xbuf) {
+        m->xbuf_bytes = xb_total(m);
+        RLB_TRY(dev_alloc((void**)&m->xbuf, m->xbuf_bytes));
+        RLB_CUDA(cudaMemset(m->xbuf, 0, m->xbuf_bytes));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) <= RLB_TP_HANDLE_BYTES, "handle does not fit");
+    cudaIpcMemHandle_t h;
+    RLB_CUDA(cudaIpcGetMemHandle(&h, m->xbuf));
+    memset(handle128, 0, RLB_TP_HANDLE_BYTES);
+    memcpy(handle128, &h, sizeof(h));
+    return RLB_OK;
+}
+
+int rlb_tp_peer_import(rlb_model* m, const void* handles, int32_t n_handles) {
+    if (!m || !handles) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import: null pointer");
+    std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
+    RLB_CUDA(cudaSetDevice(m->ctx->device));
+    if (n_handles != m->tp) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import: %d handles for %d ranks", n_handles, m->tp);
+    if (!m->xbuf) return rlb_fail(RLB_ERR_STATE, "rlb_tp_peer_import: call rlb_tp_peer_export first");
+    if (m->peers_open) return RLB_OK;
+    for (int r = 0; r < m->tp; r++) {
+        if (r == m->rank) { m->peer_xbuf[r] = m->xbuf; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)r * RLB_TP_HANDLE_BYTES, sizeof(h));
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return rlb_fail(RLB_ERR_COMM, "cannot map the exchange buffer of rank %d: %s", r, cudaGetErrorString(e));
+        m->peer_xbuf[r] = (char*)p;
+    }
+    m->peers_open = true;
+    return RLB_OK;
+}
+
 int rlb_tp_set_mode(rlb_model* m, int32_t mode) {
     if (!m) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_set_mode: null model");
-    if (mode != 0) return rlb_fail(RLB_ERR_STATE, "peer-memory exchange is not available in this build");
-    m->tp_mode = 0;
+    std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
+    if (mode != 0 && mode != 1) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_set_mode: unknown mode %d", mode);
+    if (mode == 1 && m->tp > 1 && !m->peers_open) return rlb_fail(RLB_ERR_STATE, "rlb_tp_set_mode: peer exchange buffers are not imported");
+    if (mode == 1 && !m->use_stream) return rlb_fail(RLB_ERR_STATE, "rlb_tp_set_mode: the push mode needs the staged GEMV kernels");
+    if (m->tp_mode != mode) m->graph_gen++;
+    m->tp_mode = mode;
     return RLB_OK;
 }
 
@@ -700,7 +822,8 @@ int rlb_forward(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32_t n, i
     std::lock_guard<std::recursive_mutex> g(ctx->mu);
     RLB_CUDA(cudaSetDevice(ctx->device));
     RLB_TRY(forward_common(m, c, tokens, n, start_pos, false));
-    RLB_CUDA(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->p.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    const float* logits_src = (n == 1 && push_mode(m)) ? (const float*)(m->xbuf + xb_logits(m)) : m->logits;
+    RLB_CUDA(cudaMemcpyAsync(m->h_logits, logits_src, (size_t)m->p.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 9, m->scalars + 8, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
     RLB_TRY(check_device_flag(m->h_scalars + 9));

@@ -20,7 +20,7 @@ def _device_count():
     return n.value
 
 
-def _worker(rank, world, tmpdir, f16, heads):
+def _worker(rank, world, tmpdir, f16, heads, mode):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -48,6 +48,21 @@ def _worker(rank, world, tmpdir, f16, heads):
             time.sleep(0.05)
         uid = open(id_path, "rb").read()
     m.nccl_init(uid)
+    if mode == "push":
+        # every rank maps every other rank's exchange buffer, then switches to the fused exchange
+        with open(os.path.join(tmpdir, "peer%d.tmp" % rank), "wb") as f:
+            f.write(m.peer_export())
+        os.rename(os.path.join(tmpdir, "peer%d.tmp" % rank), os.path.join(tmpdir, "peer%d.bin" % rank))
+        handles = []
+        for r in range(world):
+            path = os.path.join(tmpdir, "peer%d.bin" % r)
+            for _ in range(600):
+                if os.path.exists(path):
+                    break
+                time.sleep(0.05)
+            handles.append(open(path, "rb").read())
+        m.peer_import(handles)
+        m.set_tp_mode("push")
     S.load_into(m, cfg)
     m.finalize()
     prompt = S.synth_tokens(7, cfg["vocab"])
@@ -56,14 +71,18 @@ def _worker(rank, world, tmpdir, f16, heads):
     toks = np.load(os.path.join(tmpdir, "oracle_tokens.npy"))
     for i, t in enumerate(toks):
         outs.append(m.forward([int(t)], 7 + i, c))
-    first = m.forward_greedy(prompt, 0, m.make_caches())
+    c2 = m.make_caches()
+    first = m.forward_greedy(prompt, 0, c2)
+    dev_tokens, _ = m.decode_greedy(first, 7, 5, c2)  # graph replays with on-device feedback
+    np.save(os.path.join(tmpdir, "dev_tokens_rank%d.npy" % rank), dev_tokens)
     np.save(os.path.join(tmpdir, "logits_rank%d.npy" % rank), np.stack(outs))
     np.save(os.path.join(tmpdir, "first_rank%d.npy" % rank), np.array([first]))
     cl.flush()
 
 
-@pytest.mark.parametrize("f16,heads", [(False, 4), (True, 4), (True, 3)])
-def test_tp2_matches_oracle(tmp_path, f16, heads):
+@pytest.mark.parametrize("f16,heads,mode", [(False, 4, "nccl"), (True, 4, "nccl"), (True, 3, "nccl"),
+                                            (False, 4, "push"), (True, 4, "push"), (True, 3, "push")])
+def test_tp2_matches_oracle(tmp_path, f16, heads, mode):
     if _device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -79,7 +98,7 @@ def test_tp2_matches_oracle(tmp_path, f16, heads):
         toks.append(int(np.argmax(want[-1])))
         want.append(orc.forward([toks[-1]], 7 + i, oc))
     np.save(str(tmp_path / "oracle_tokens.npy"), np.array(toks, dtype=np.int32))
-    mp.spawn(_worker, args=(2, str(tmp_path), f16, heads), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, str(tmp_path), f16, heads, mode), nprocs=2, join=True)
     r0 = np.load(str(tmp_path / "logits_rank0.npy")); r1 = np.load(str(tmp_path / "logits_rank1.npy"))
     assert np.array_equal(r0, r1)  # every rank holds the same logits, bit for bit
     want = np.stack(want)
@@ -88,3 +107,7 @@ def test_tp2_matches_oracle(tmp_path, f16, heads):
     else:
         assert float(np.abs(r0 - want).max() / np.abs(want).max()) <= 1e-4
     assert int(np.load(str(tmp_path / "first_rank0.npy"))[0]) == int(np.load(str(tmp_path / "first_rank1.npy"))[0])
+    d0 = np.load(str(tmp_path / "dev_tokens_rank0.npy")); d1 = np.load(str(tmp_path / "dev_tokens_rank1.npy"))
+    assert np.array_equal(d0, d1)
+    if not f16:  # f32: the device loop must follow the oracle's greedy continuation exactly
+        assert d0[:3].tolist() == toks[1:4]
