@@ -87,9 +87,19 @@ __device__ __forceinline__ void argmax_block(const float* logits, int n, float& 
     __shared__ int si[32];
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = __ldcg(logits + i);
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    // eight loads in flight per thread: the vector is read once, latency is all that matters
+    for (int base = threadIdx.x; base < n; base += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = base + j * blockDim.x;
+            v[j] = i < n ? __ldcg(logits + i) : -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = base + j * blockDim.x;
+            if (i < n && (v[j] > bv || (v[j] == bv && i < bi))) { bv = v[j]; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

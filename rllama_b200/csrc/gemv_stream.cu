@@ -178,6 +178,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         return;
     }
 
+    // RMSNorm gains never change: fetch this thread's share before waiting for the previous kernel
+    constexpr int kGainRegs = 32;
+    float gain_r[kGainRegs];
+    if (PRO == PRO_NORM && warp < kConsumerWarps) {
+#pragma unroll
+        for (int q = 0; q < kGainRegs; q++) {
+            const int i = tid + q * kConsumers;
+            gain_r[q] = i < K ? a.gain[i] : 0.f;
+        }
+    }
+
     pdl_wait();  // everything below reads or overwrites what earlier kernels use
 
     if (warp == kConsumerWarps + 1) {
@@ -305,7 +316,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
         const float scale = 1.0f / sqrtf(tot / (float)K + a.eps);
-        for (int i = tid; i < K; i += kConsumers) act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), a.gain[i]));
+#pragma unroll
+        for (int q = 0; q < kGainRegs; q++) {
+            const int i = tid + q * kConsumers;
+            if (i < K) act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), gain_r[q]));
+        }
+        for (int i = tid + kGainRegs * kConsumers; i < K; i += kConsumers)
+            act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), a.gain[i]));
     }
     consumer_sync();
 
