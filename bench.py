@@ -321,12 +321,13 @@ def main():
         peak, peak_kind = measured_peak_gbs()
         achieved = alg / (ms_per_token * 1e-3) / 1e9 / world  # per GPU
         traffic = None
-        tp = os.path.join(ROOT, "profiles", "decode_step_traffic.json")
+        tp = os.path.join(ROOT, "profiles", "decode_step_7b_f16_traffic.txt")
         if os.path.exists(tp) and args.workload == "7b" and world == 1 and not args.layers:
-            try:
-                traffic = json.load(open(tp)).get("dram_bytes_per_token")
-            except Exception:
-                traffic = None
+            # dram__bytes_read.sum + dram__bytes_write.sum per decoded token, from the ncu capture
+            # summarised beside that file
+            for ln in open(tp):
+                if ln.startswith("dram_bytes_per_token"):
+                    traffic = int(ln.split("=")[1])
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": ms_per_token, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

@@ -19,6 +19,12 @@ int rlb_fail(int code, const char* fmt, ...) {
     return code;
 }
 
+int ctx_check_error_word(rlb_ctx* ctx) {
+    if (ctx && ctx->h_err && *reinterpret_cast<volatile int*>(ctx->h_err) != 0)
+        return rlb_fail(RLB_ERR_CUDA, "a kernel gave up on a bounded wait (code %d); results on this context are invalid", *ctx->h_err);
+    return RLB_OK;
+}
+
 extern "C" {
 
 const char* rlb_last_error(void) { return g_err; }
@@ -62,9 +68,16 @@ int rlb_ctx_create(int verbose, int nth_device, rlb_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->verbose = verbose != 0;
     cudaError_t se = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (se == cudaSuccess) se = cudaHostAlloc((void**)&ctx->h_err, 64, cudaHostAllocMapped);
+    if (se == cudaSuccess) {
+        *ctx->h_err = 0;
+        se = cudaHostGetDevicePointer((void**)&ctx->d_err, ctx->h_err, 0);
+    }
     if (se != cudaSuccess) {
+        if (ctx->stream) cudaStreamDestroy(ctx->stream);
+        if (ctx->h_err) cudaFreeHost(ctx->h_err);
         delete ctx;
-        return rlb_fail(RLB_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(se));
+        return rlb_fail(RLB_ERR_CUDA, "context set-up: %s", cudaGetErrorString(se));
     }
     *out = ctx;
     return RLB_OK;
@@ -75,6 +88,7 @@ int rlb_ctx_destroy(rlb_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->op_scratch) cudaFree(ctx->op_scratch);
+    if (ctx->h_err) cudaFreeHost(ctx->h_err);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RLB_OK;
@@ -85,7 +99,7 @@ int rlb_ctx_flush(rlb_ctx* ctx) {
     std::lock_guard<std::recursive_mutex> g(ctx->mu);
     RLB_CUDA(cudaSetDevice(ctx->device));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
-    return RLB_OK;
+    return ctx_check_error_word(ctx);
 }
 
 int rlb_ctx_kernel_launches(rlb_ctx* ctx, uint64_t* count) {
@@ -155,7 +169,7 @@ int rlb_tensor_zeros(rlb_ctx* ctx, int64_t rows, int64_t cols, int64_t capacity_
 int rlb_tensor_wait(rlb_tensor* t) {
     if (!t) return rlb_fail(RLB_ERR_INVALID, "rlb_tensor_wait: null tensor");
     RLB_CUDA(cudaEventSynchronize(t->ready));
-    return RLB_OK;
+    return ctx_check_error_word(t->ctx);
 }
 
 int rlb_tensor_download(rlb_tensor* t, void* host, rlb_event** out_event) {
@@ -180,10 +194,11 @@ int rlb_tensor_download(rlb_tensor* t, void* host, rlb_event** out_event) {
 int rlb_event_wait(rlb_event* ev) {
     if (!ev) return rlb_fail(RLB_ERR_INVALID, "rlb_event_wait: null event");
     cudaError_t e = cudaEventSynchronize(ev->ev);
+    rlb_ctx* ctx = ev->ctx;
     cudaEventDestroy(ev->ev);
     delete ev;
     if (e != cudaSuccess) return rlb_fail(RLB_ERR_CUDA, "event wait: %s", cudaGetErrorString(e));
-    return RLB_OK;
+    return ctx_check_error_word(ctx);
 }
 
 int rlb_tensor_free(rlb_tensor* t) {

@@ -8,7 +8,17 @@
 // fallback shape-generic path for f16.
 #include "internal.h"
 
+#include <cstdlib>
+
 namespace {
+
+// The tensor-core kernel takes f16 GEMMs with at least this many rows on the token side.
+constexpr int kTcMinRows = 16;
+bool tc_enabled() {
+    static const bool on = getenv("RLB_GEMM_TC") == nullptr || atoi(getenv("RLB_GEMM_TC")) != 0;
+    return on;
+}
+
 
 constexpr int BM = 64;  // rows of A per CTA
 constexpr int BN = 64;  // rows of W per CTA
@@ -76,7 +86,9 @@ __global__ void __launch_bounds__(256) gemm_nt_kernel(const T* __restrict__ A, i
 }  // namespace
 
 int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, float* C, int64_t ldc, int n,
-                   int M, int K, int round_out) {
+                   int M, int K, int round_out, int* err) {
+    if (dtype == RLB_F16 && tc_enabled() && n >= kTcMinRows && gemm_tc_supported(A, lda, W, ldw, n, M, K))
+        return launch_gemm_tc_f32out(ctx, A, lda, W, ldw, C, ldc, n, M, K, round_out, err ? err : ctx->d_err);
     dim3 grid((M + BN - 1) / BN, (n + BM - 1) / BM);
     if (grid.y > 65535) return rlb_fail(RLB_ERR_LIMIT, "gemm: too many rows (%d)", n);
     if (dtype == RLB_F16) {
@@ -92,6 +104,8 @@ int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, co
 
 int launch_gemm_nt_typed(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                          int n, int M, int K) {
+    if (dtype == RLB_F16 && tc_enabled() && n >= kTcMinRows && gemm_tc_supported(A, lda, W, ldw, n, M, K))
+        return launch_gemm_tc_f16out(ctx, A, lda, W, ldw, C, ldc, n, M, K, ctx->d_err);
     dim3 grid((M + BN - 1) / BN, (n + BM - 1) / BM);
     if (grid.y > 65535) return rlb_fail(RLB_ERR_LIMIT, "gemm: too many rows (%d)", n);
     if (dtype == RLB_F16)

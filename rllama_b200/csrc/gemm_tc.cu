@@ -1,0 +1,282 @@
+// Prefill contraction on the 5th-generation tensor cores: C[n][M] = X[n][K] * W[M][K]^T for f16
+// operands with f32 accumulation -- rllama's batched Tensor::matrix_mul_transposed
+// (src/tensor.rs:999-1025, f16 branch :1476-1666; OpenCL kernel matrix_mul_transposed_f16,
+// src/tensor_opencl_support.rs:512-557), the only dense contraction on the path.
+//
+// One CTA computes a 128 (weight rows) x BN (tokens) tile:
+//  * operands arrive by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the
+//    tensor) into a 4-stage shared-memory ring; one thread issues the loads;
+//  * one thread issues tcgen05.mma (kind::f16, M 128, N BN, K 16 per instruction, four per
+//    64-column stage) with the accumulator in tensor memory; tcgen05.commit releases a ring
+//    slot when the MMAs that read it have finished;
+//  * four warps read the accumulator back with tcgen05.ld (each warp owns 32 TMEM lanes = 32
+//    weight rows), round to f16 where the reference rounds the GEMM result, and store
+//    token-major so that a warp writes 128 contiguous bytes per token.
+// Products of f16 values are exact in f32; only the summation order differs from the
+// reference's 8-lane FMA scheme.
+//
+// Every mbarrier wait is bounded; on a timeout the kernel raises the error word and still
+// releases its tensor memory before returning.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "internal.h"
+
+namespace {
+
+constexpr int BM = 128;       // weight rows per tile (MMA M)
+constexpr int BK = 64;        // K columns per stage: 128 bytes of f16 = one swizzle span
+constexpr int kStages = 4;
+constexpr int kTcThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait; false when it ran out (the error word is raised).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead, int* err) {
+    for (uint32_t i = 0; i < kWaitLimit; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *dead) return false;
+    }
+    *dead = 1;
+    *reinterpret_cast<volatile int*>(err) = 3;  // plain store: the word may live in mapped host memory
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset
+    d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                         // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <typename OT> __device__ __forceinline__ OT out_cast(float v);
+template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return __float2half_rn(v); }
+
+template <int BN, typename OT>
+__global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                             const __grid_constant__ CUtensorMap tm_x, OT* __restrict__ C, int64_t ldc,
+                                                             int n, int Mrows, int K, int round_out, int* err) {
+    constexpr uint32_t A_BYTES = BM * BK * 2;
+    constexpr uint32_t B_BYTES = BN * BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int dead_flag;
+    volatile int* dead = &dead_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;  // first weight row of the tile
+    const int n0 = blockIdx.y * BN;  // first token of the tile
+    const int nkb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        dead_flag = 0;
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {  // one warp allocates the accumulator's tensor memory
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % kStages;
+            const uint32_t ph = (kb / kStages) & 1u;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
+            unsigned char* a_s = tiles + (size_t)s * STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(a_s, &tm_w, kb * BK, m0, &full_bar[s]);
+            tma_load_2d(a_s + A_BYTES, &tm_x, kb * BK, n0, &full_bar[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        // instruction descriptor: f32 accumulator, f16 A and B, both K-major, N = BN, M = 128
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        bool ok = true;
+        for (int kb = 0; kb < nkb && ok; kb++) {
+            const int s = kb % kStages;
+            const uint32_t ph = (kb / kStages) & 1u;
+            ok = mbar_wait(&full_bar[s], ph, dead, err);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+            const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / 16; k++) {
+                // 16 K columns = 32 bytes further along the swizzled row
+                umma_f16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[s]);  // the slot is free once these MMAs have read it
+        }
+        umma_commit(&done_bar);
+    }
+
+    // ---------------- epilogue: warps 2..5, one TMEM lane quarter each ----------------
+    if (warp >= 2) {
+        const bool ok = mbar_wait(&done_bar, 0, dead, err);
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3;
+        const int row = m0 + q * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                      "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int token = n0 + c0 + j;
+                    if (token < n && row < Mrows) {
+                        float v = __uint_as_float(r[j]);
+                        if (round_out) v = __half2float(__float2half_rn(v));
+                        C[(int64_t)token * ldc + row] = out_cast<OT>(v);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+int load_encode() {
+    if (g_encode) return RLB_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+        return rlb_fail(RLB_ERR_CUDA, "cuTensorMapEncodeTiled is not available: %s", cudaGetErrorString(e));
+    g_encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    return RLB_OK;
+}
+
+// f16 row-major [rows][K] with row stride ld elements; box = 64 columns x box_rows rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return rlb_fail(RLB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return RLB_OK;
+}
+
+template <int BN, typename OT>
+int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, OT* C, int64_t ldc, int n, int M, int K, int round_out, int* err) {
+    auto kern = gemm_tc_kernel<BN, OT>;
+    const size_t smem = (size_t)kStages * (BM * BK * 2 + BN * BK * 2) + 1024;
+    static bool set = false;
+    if (!set) {
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set = true;
+    }
+    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN);
+    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, C, ldc, n, M, K, round_out, err);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    return RLB_OK;
+}
+
+template <typename OT>
+int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
+              int* err) {
+    RLB_TRY(load_encode());
+    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
+    CUtensorMap tw, tx;
+    RLB_TRY(make_map(&tw, W, M, K, ldw, BM));
+    RLB_TRY(make_map(&tx, X, n, K, ldx, bn));
+    switch (bn) {
+        case 256: return launch_bn<256, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
+        case 128: return launch_bn<128, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
+        case 64: return launch_bn<64, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
+        default: return launch_bn<32, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
+    }
+}
+
+}  // namespace
+
+// True when the tensor-core kernel takes these operands: 16-byte aligned bases and row strides.
+bool gemm_tc_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, int n, int M, int K) {
+    if (n < 1 || M < 1 || K < 8) return false;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
+    if ((ldx * 2) % 16 != 0 || (ldw * 2) % 16 != 0) return false;
+    return true;
+}
+
+int launch_gemm_tc_f32out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M, int K,
+                          int round_out, int* err) {
+    return launch_tc<float>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+}
+
+int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, void* C, int64_t ldc, int n, int M, int K,
+                          int* err) {
+    return launch_tc<__half>(ctx, X, ldx, W, ldw, reinterpret_cast<__half*>(C), ldc, n, M, K, 0, err);
+}

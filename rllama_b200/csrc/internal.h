@@ -44,7 +44,12 @@ struct rlb_ctx {
     uint64_t launches = 0;  // kernels launched by this library on this context
     void* op_scratch = nullptr;  // scratch of the standalone attention op, grown on demand
     size_t op_scratch_bytes = 0;
+    // error word of the op-level kernels: mapped pinned host memory, so the host reads it after a
+    // synchronisation without a copy (raised when a bounded device-side wait ran out)
+    int* h_err = nullptr;
+    int* d_err = nullptr;
 };
+int ctx_check_error_word(rlb_ctx* ctx);  // after a synchronisation: RLB_ERR_CUDA if a kernel raised the word
 
 struct rlb_tensor {
     rlb_ctx* ctx = nullptr;
@@ -192,11 +197,19 @@ int launch_cache_shift_left(rlb_ctx* ctx, void* cache, rlb_dtype dtype, int64_t 
 // ---------------------------------------------------------------------------------------
 // prefill GEMM (gemm.cu): C[n][M] f32 = A[n][K] * W[M][K]^T, optional f16 rounding of the result
 // ---------------------------------------------------------------------------------------
+// err: device-visible error word for the tensor-core path (nullptr: the context's word).
 int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, float* C,
-                   int64_t ldc, int n, int M, int K, int round_out);
+                   int64_t ldc, int n, int M, int K, int round_out, int* err = nullptr);
 // Same contraction, output stored in the operand dtype (tier-1 op).
 int launch_gemm_nt_typed(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, void* C,
                          int64_t ldc, int n, int M, int K);
+
+// tcgen05 tile kernel for f16 operands (gemm_tc.cu)
+bool gemm_tc_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, int n, int M, int K);
+int launch_gemm_tc_f32out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M,
+                          int K, int round_out, int* err);
+int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, void* C, int64_t ldc, int n, int M,
+                          int K, int* err);
 
 // ---------------------------------------------------------------------------------------
 // helpers

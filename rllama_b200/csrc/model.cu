@@ -397,21 +397,21 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         // q, k, v as three GEMMs into contiguous [n][nq] blocks
         for (int s = 0; s < 3; s++)
             RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, (char*)W.wqkv + (size_t)s * nq * d * m->wsz, d,
-                                   m->pf_qkv + (size_t)s * n * nq, nq, n, nq, d, f16));
+                                   m->pf_qkv + (size_t)s * n * nq, nq, n, nq, d, f16, m->scalars + 8));
         RLB_TRY(launch_rope_append(ctx, m->pf_qkv, m->pf_qkv + (size_t)n * nq, m->pf_qkv + (size_t)2 * n * nq, n, start_pos, m->nh,
                                    m->hd, m->p.max_seq_len, m->rope, m->wdt, kc, vc));
         AttnPrefillArgs aa;
         aa.q = m->pf_qkv; aa.kcache = kc; aa.vcache = vc; aa.out = m->pf_o; aa.n = n; aa.start_pos = start_pos;
         aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len;
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, F, n, F, d, f16));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w3, d, m->pf_g3, F, n, F, d, f16));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, F, n, F, d, f16, m->scalars + 8));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w3, d, m->pf_g3, F, n, F, d, f16, m->scalars + 8));
         RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g3, (int64_t)n * F, m->wdt, m->pf_g));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj, m->scalars + 8));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
     }
@@ -427,6 +427,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
 
 // The decode kernels raise scalars[8] when a bounded wait ran out; h points at its host copy.
 int check_device_flag(const int32_t* h) {
+    if (*h == 3) return rlb_fail(RLB_ERR_CUDA, "the prefill GEMM gave up waiting on a shared-memory barrier (results are invalid)");
     if (*h == 2) return rlb_fail(RLB_ERR_COMM, "a decode kernel gave up waiting for another rank's partial sums (results are invalid)");
     if (*h != 0) return rlb_fail(RLB_ERR_CUDA, "a decode kernel gave up waiting on a shared-memory barrier (results are invalid)");
     return RLB_OK;
