@@ -305,13 +305,15 @@ def main():
         c2.free()
 
     kernels = None
-    if args.profile_kernels and rank == 0 and world == 1:
+    if args.profile_kernels:
+        # eager pass with events around every kernel class (all ranks run it; rank 0 reports). Under
+        # tensor parallelism a class's time includes waiting for the other ranks' partial sums.
         model.set_option("profile", 1)
         c3 = model.make_caches()
         f3 = model.forward_greedy(prompt, 0, c3)
         model.decode_greedy(f3, P, 16, c3)
         n = model.get_stat("prof_steps")
-        kernels = {k: model.get_stat("prof_ms_" + k) / n for k in ("qkv", "attn", "wo", "w13", "w2", "head", "argmax")}
+        kernels = {k: model.get_stat("prof_ms_" + k) / n for k in ("qkv", "attn", "wo", "w13", "w2", "head", "argmax", "comm")}
         model.set_option("profile", 0)
         c3.free()
 

@@ -79,26 +79,51 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
         x[i] += do_round ? round_f16(y[i]) : y[i];
 }
 
+// Bounded poll of one {value, sequence} entry of the tensor-parallel exchange.
+__device__ __forceinline__ bool ll_poll(const uint2* p, uint32_t seq, float& out) {
+    for (uint32_t i = 0; i < (1u << 20); i++) {
+        uint32_t v, f;
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(p) : "memory");
+        if (f == seq) { out = __uint_as_float(v); return true; }
+    }
+    out = 0.f;
+    return false;
+}
+
 // Greedy choice = TokenSampler with top_k 1 (src/token_sampler.rs:20-28, :127-147): the
 // largest logit; among equal maxima the lowest id (the reference's unstable sort leaves ties
 // unspecified). NaNs sort last, as in the reference's comparator.
-__device__ __forceinline__ void argmax_block(const float* logits, int n, float& best_v, int& best_i) {
+// In tensor-parallel push mode the logits arrive as {value, sequence} entries from every rank's
+// head kernel; they are polled here (bounded) and unpacked into the dense logits array.
+__device__ __forceinline__ void argmax_block(const float* logits, int n, const StepSync& sy, float& best_v, int& best_i) {
     __shared__ float sv[32];
     __shared__ int si[32];
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    // eight loads in flight per thread: the vector is read once, latency is all that matters
-    for (int base = threadIdx.x; base < n; base += 8 * blockDim.x) {
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const int i = base + j * blockDim.x;
-            v[j] = i < n ? __ldcg(logits + i) : -INFINITY;
+    if (sy.ll_logits != nullptr) {
+        const uint32_t seq = (uint32_t)(*sy.epoch - 1) * sy.seq_stride + sy.seq_idx;
+        bool ok = true;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            float v;
+            ok = ll_poll(sy.ll_logits + i, seq, v) && ok;
+            sy.dense_out[i] = v;
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
+        if (!ok) atomicExch(sy.err, 2);
+    } else {
+        // eight loads in flight per thread: the vector is read once, latency is all that matters
+        for (int base = threadIdx.x; base < n; base += 8 * blockDim.x) {
+            float v[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const int i = base + j * blockDim.x;
-            if (i < n && (v[j] > bv || (v[j] == bv && i < bi))) { bv = v[j]; bi = i; }
+            for (int j = 0; j < 8; j++) {
+                const int i = base + j * blockDim.x;
+                v[j] = i < n ? __ldcg(logits + i) : -INFINITY;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int i = base + j * blockDim.x;
+                if (i < n && (v[j] > bv || (v[j] == bv && i < bi))) { bv = v[j]; bi = i; }
+            }
         }
     }
 #pragma unroll
@@ -116,29 +141,9 @@ __device__ __forceinline__ void argmax_block(const float* logits, int n, float& 
     best_v = bv; best_i = bi;
 }
 
-// Tensor-parallel push mode: the logits are written into this GPU's memory by every rank's head
-// kernel; wait (bounded) until all of them have counted themselves in for this step.
-__device__ __forceinline__ void step_wait(const StepSync& sy) {
-    if (sy.wait_flag != nullptr) {
-        if (threadIdx.x == 0) {
-            const unsigned long long target = (unsigned long long)(*sy.epoch) * sy.wait_per_epoch;
-            bool ok = false;
-            for (unsigned int i = 0; i < (1u << 22); i++) {
-                unsigned long long v;
-                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(sy.wait_flag) : "memory");
-                if (v >= target) { ok = true; break; }
-            }
-            if (!ok) atomicExch(sy.err, 2);
-        }
-        __syncthreads();
-    }
-}
-
-// logits may have been written by other GPUs: read them through L2
 __global__ void argmax_kernel(const float* logits, int n, int32_t* __restrict__ out_tok, const StepSync sy) {
-    step_wait(sy);
     float bv; int bi;
-    argmax_block(logits, n, bv, bi);
+    argmax_block(logits, n, sy, bv, bi);
     if (threadIdx.x == 0) {
         *out_tok = bi;
         if (sy.epoch) *sy.epoch = *sy.epoch + 1;
@@ -147,9 +152,8 @@ __global__ void argmax_kernel(const float* logits, int n, int32_t* __restrict__ 
 
 __global__ void argmax_advance_kernel(const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step,
                                       int32_t* tokens_out, int32_t cap, const StepSync sy) {
-    step_wait(sy);
     float bv; int bi;
-    argmax_block(logits, n, bv, bi);
+    argmax_block(logits, n, sy, bv, bi);
     if (threadIdx.x == 0) {
         if (sy.epoch) *sy.epoch = *sy.epoch + 1;
         *tok = bi;

@@ -200,11 +200,7 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a) {
 #pragma unroll
             for (int r = 0; r < R; r++)
                 if (lane == r) {
-                    if (a.n_outs == 0) {
-                        reinterpret_cast<float*>(a.out)[(int64_t)(row0 + r) * a.out_stride] = acc[0][r];
-                    } else {
-                        for (int d = 0; d < a.n_outs; d++) a.outs[d][a.out_offset + row0 + r] = acc[0][r];
-                    }
+                    reinterpret_cast<float*>(a.out)[(int64_t)(row0 + r) * a.out_stride] = acc[0][r];
                 }
         } else if (EPI == EPI_SWIGLU) {
             WT* out = reinterpret_cast<WT*>(a.out);
@@ -246,12 +242,6 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a) {
         }
     }
 
-    if (EPI == EPI_F32 && a.n_outs > 0 && a.flags[0] != nullptr) {
-        // push mode: make this CTA's remote stores visible, then count it in at every destination
-        __threadfence_system();
-        __syncthreads();
-        if (tid < a.n_outs) atomicAdd_system(a.flags[tid], 1ull);
-    }
 }
 
 struct Tuning {

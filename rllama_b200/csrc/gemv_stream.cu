@@ -72,6 +72,39 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Tensor-parallel exchange entries: {f32 value, u32 sequence number} in one 8-byte store.
+__device__ __forceinline__ void ll_store(uint2* p, float v, uint32_t seq) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+// Bounded poll of up to N entries (base + j * stride, j < count) until each carries `seq`. All
+// pending entries are requested before any is examined, so one round costs one memory round
+// trip. On a timeout the missing values read as 0, *dead is set and the error word raised.
+template <int N>
+__device__ __forceinline__ void ll_gather(const uint2* base, size_t stride, int count, uint32_t seq, float (&v)[N], volatile int* dead,
+                                          int* err) {
+    uint32_t pend = count >= N ? ((N == 32) ? 0xffffffffu : ((1u << N) - 1u)) : ((1u << count) - 1u);
+#pragma unroll
+    for (int j = 0; j < N; j++) v[j] = 0.f;
+    for (uint32_t it = 0; pend != 0 && it < (1u << 20); it++) {
+        uint32_t vv[N], ff[N];
+#pragma unroll
+        for (int j = 0; j < N; j++)
+            if (pend & (1u << j))
+                asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(vv[j]), "=r"(ff[j]) : "l"(base + (size_t)j * stride) : "memory");
+#pragma unroll
+        for (int j = 0; j < N; j++)
+            if ((pend & (1u << j)) && ff[j] == seq) {
+                v[j] = __uint_as_float(vv[j]);
+                pend &= ~(1u << j);
+            }
+        if ((it & 255u) == 255u && *dead) return;
+    }
+    if (pend != 0) {
+        *dead = 1;
+        atomicExch(err, 2);
+    }
+}
+
 __device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
 template <typename T> __device__ __forceinline__ T cast_to(float v);
 template <> __device__ __forceinline__ __half cast_to<__half>(float v) { return __float2half_rn(v); }
@@ -224,7 +257,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                     if (a.n_outs == 0) {
                         reinterpret_cast<float*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = v;
                     } else {
-                        for (int d = 0; d < a.n_outs; d++) a.outs[d][a.out_offset + row0 + lane] = v;
+                        // push this partial sum, tagged with the exchange's sequence number, into every rank's inbox
+                        const uint32_t seq = (uint32_t)(*a.epoch_ptr - 1) * a.seq_stride + a.out_seq_idx;
+                        for (int d = 0; d < a.n_outs; d++) ll_store(a.ll_outs[d] + a.out_offset + row0 + lane, v, seq);
                     }
                 }
             } else if (EPI == EPI_SWIGLU) {
@@ -258,12 +293,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                 }
             }
         }
-        if (EPI == EPI_F32 && a.n_outs > 0 && a.flags[0] != nullptr) {
-            // push mode: this warp made all of the CTA's remote stores
-            __threadfence_system();
-            __syncwarp();
-            if (lane < a.n_outs) atomicAdd_system(a.flags[lane], 1ull);
-        }
         return;
     }
 
@@ -273,41 +302,59 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         uint4* dst = reinterpret_cast<uint4*>(act);
         for (int i = tid; i < K / VEC; i += kConsumers) dst[i] = src[i];
     } else {
-        if (a.wait_flag != nullptr) {
-            // tensor-parallel push mode: every rank's projection kernel stores its partial sums
-            // into this GPU's inbox and then counts its CTAs in; wait (bounded) for all of them
-            if (tid == 0) {
-                const unsigned long long target = (unsigned long long)(*a.epoch_ptr) * a.wait_per_epoch;
-                bool ok = false;
-                for (uint32_t i = 0; i < (1u << 22) && !*dead; i++) {
-                    unsigned long long v;
-                    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(a.wait_flag) : "memory");
-                    if (v >= target) { ok = true; break; }
-                }
-                if (!ok) { *dead = 1; atomicExch(cfg.err, 2); }
-            }
-            consumer_sync();
-        }
         const float* xin = a.x_in;
         if (a.tok_ptr) xin += (int64_t)(*a.tok_ptr) * K;
         float ss = 0.f;
-        for (int i = tid * 4; i < K; i += kConsumers * 4) {
-            float4 v = *reinterpret_cast<const float4*>(xin + i);
-            if (a.n_parts > 0) {
-                // the partial sums may come from other GPUs: read them through L2
-                float4 sacc = __ldcg(reinterpret_cast<const float4*>(a.parts + i));
-                for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
-                    const float4 t = __ldcg(reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i));
-                    sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
-                }
-                if (a.round_parts) {
-                    sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
-                }
-                v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+        if (a.ll_inbox != nullptr) {
+            // Tensor-parallel push exchange. This CTA owns a slice of the residual row: it collects
+            // that slice's partial sums from every rank's entries (rank order, f16 rounding after the
+            // sum), adds the residual and publishes the result as {value, sequence} entries; then
+            // every CTA reads the whole new residual from those entries. The sequence numbers carry
+            // the ordering: no fence, no grid barrier.
+            const uint32_t seq = (uint32_t)(*a.epoch_ptr - 1) * a.seq_stride + a.seq_idx;
+            const int per = ((K + (int)gridDim.x - 1) / (int)gridDim.x + 3) & ~3;
+            const int s0 = min(K, (int)blockIdx.x * per), s1 = min(K, s0 + per);
+            for (int i = s0 + tid; i < s1; i += kConsumers) {
+                float part[RLB_MAX_TP];
+                ll_gather<RLB_MAX_TP>(a.ll_inbox + i, (size_t)K, a.n_parts, seq, part, dead, cfg.err);
+                float sum = part[0];
+#pragma unroll
+                for (int q = 1; q < RLB_MAX_TP; q++)
+                    if (q < a.n_parts) sum += part[q];  // fixed rank order: identical on every rank
+                if (a.round_parts) sum = round_f16(sum);
+                const float v = xin[i] + sum;
+                if (a.x_out) a.x_out[i] = v;
+                ll_store(a.ll_x + i, v, seq);
             }
-            *reinterpret_cast<float4*>(tmp + i) = v;
-            if (blockIdx.x == 0 && a.x_out) *reinterpret_cast<float4*>(a.x_out + i) = v;
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            for (int base = tid; base < K; base += 8 * kConsumers) {
+                float v8[8];
+                const int cnt = min(8, (K - base + kConsumers - 1) / kConsumers);
+                ll_gather<8>(a.ll_x + base, (size_t)kConsumers, cnt, seq, v8, dead, cfg.err);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (j < cnt) {
+                        tmp[base + j * kConsumers] = v8[j];
+                        ss = fmaf(v8[j], v8[j], ss);
+                    }
+            }
+        } else {
+            for (int i = tid * 4; i < K; i += kConsumers * 4) {
+                float4 v = *reinterpret_cast<const float4*>(xin + i);
+                if (a.n_parts > 0) {
+                    float4 sacc = *reinterpret_cast<const float4*>(a.parts + i);
+                    for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
+                        const float4 t = *reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i);
+                        sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
+                    }
+                    if (a.round_parts) {
+                        sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
+                    }
+                    v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+                }
+                *reinterpret_cast<float4*>(tmp + i) = v;
+                if (blockIdx.x == 0 && a.x_out) *reinterpret_cast<float4*>(a.x_out + i) = v;
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
         }
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;

@@ -103,13 +103,16 @@ struct GemvArgs {
     // epilogue
     void* out = nullptr;
     int64_t out_stride = 1;
-    float* outs[RLB_MAX_TP] = {nullptr};  // EPI_F32 push mode: per-destination base pointers (may be peer memory)
+    // Tensor-parallel push exchange. Values travel as 8-byte {f32 value, u32 sequence number}
+    // entries written with one store, so a reader that sees the expected sequence number also
+    // sees the value: no fence and no separate flag. The sequence number of an exchange is
+    // (*epoch_ptr - 1) * seq_stride + seq_idx, unique per (decode step, layer, projection).
+    uint2* ll_outs[RLB_MAX_TP] = {nullptr};  // EPI_F32 producer: every rank's inbox (peer memory); entry = out_offset + row
     int n_outs = 0;                  // 0: write `out` only
-    int64_t out_offset = 0;          // added to row for pushed writes
-    unsigned long long* flags[RLB_MAX_TP] = {nullptr};  // per-destination arrival counters (push mode)
-    // PRO_NORM in push mode: before reading `parts`, wait until *wait_flag >= *epoch_ptr * wait_per_epoch
-    const unsigned long long* wait_flag = nullptr;
-    unsigned long long wait_per_epoch = 0;
+    int64_t out_offset = 0;
+    const uint2* ll_inbox = nullptr; // PRO_NORM consumer: this rank's inbox, n_parts x K entries
+    uint2* ll_x = nullptr;           // PRO_NORM consumer: K entries where slice owners publish the new residual
+    uint32_t seq_idx = 0, seq_stride = 0, out_seq_idx = 0;
     const int32_t* epoch_ptr = nullptr;
     // EPI_QKV
     float* qbuf = nullptr;
@@ -176,10 +179,11 @@ int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int r
 // Optional wait of the arg-max kernels for pushed logits (tensor-parallel push mode), and the
 // per-step epoch counter they advance.
 struct StepSync {
-    const unsigned long long* wait_flag = nullptr;  // wait until *wait_flag >= *epoch * wait_per_epoch
-    unsigned long long wait_per_epoch = 0;
-    int32_t* epoch = nullptr;                       // incremented once per decode step (if set)
-    int32_t* err = nullptr;                         // raised when the wait runs out
+    const uint2* ll_logits = nullptr;  // push mode: {value, sequence} entries written by every rank's head kernel
+    float* dense_out = nullptr;        // ... unpacked here while they are polled
+    uint32_t seq_idx = 0, seq_stride = 0;
+    int32_t* epoch = nullptr;          // incremented once per decode step (if set)
+    int32_t* err = nullptr;            // raised when a poll runs out
 };
 int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok, const StepSync& sync = StepSync());
 // greedy feedback: tok <- argmax, pos <- pos + 1, tokens_out[step] <- tok, step <- step + 1

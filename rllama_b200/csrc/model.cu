@@ -96,8 +96,9 @@ struct rlb_model {
     // tensor parallel
     TpNccl nccl;
     int tp_mode = 0;                 // 0: NCCL collectives, 1: fused one-shot push over peer memory
-    // push mode: one exchange buffer per rank, mapped into every peer
-    //   [inbox_wo : tp*dim f32][inbox_w2 : tp*dim f32][logits : vocab f32][flags : (2*L+1) x 16 u64]
+    // push mode: one exchange buffer per rank, mapped into every peer; all of it is 8-byte
+    // {f32 value, u32 sequence} entries:
+    //   [inbox_wo : tp*dim][inbox_w2 : tp*dim][logits : vocab][x_a : dim][x_b : dim]
     char* xbuf = nullptr;
     size_t xbuf_bytes = 0;
     char* peer_xbuf[RLB_MAX_TP] = {nullptr};  // peer_xbuf[rank] == xbuf
@@ -168,13 +169,12 @@ void prof_collect(rlb_model* m) {
     m->prof_steps++;
 }
 
-// Exchange-buffer layout (push mode).
+// Exchange-buffer layout (push mode), byte offsets.
 size_t xb_inbox_wo(const rlb_model*) { return 0; }
-size_t xb_inbox_w2(const rlb_model* m) { return (size_t)m->tp * m->p.dim * 4; }
-size_t xb_logits(const rlb_model* m) { return 2 * (size_t)m->tp * m->p.dim * 4; }
-size_t xb_flags(const rlb_model* m) { return (xb_logits(m) + (size_t)m->p.vocab_size * 4 + 255) & ~(size_t)255; }
-size_t xb_flag(const rlb_model* m, int index) { return xb_flags(m) + (size_t)index * 128; }  // one 128-byte line each
-size_t xb_total(const rlb_model* m) { return xb_flag(m, 2 * m->p.n_layers + 1); }
+size_t xb_inbox_w2(const rlb_model* m) { return (size_t)m->tp * m->p.dim * 8; }
+size_t xb_logits(const rlb_model* m) { return 2 * (size_t)m->tp * m->p.dim * 8; }
+size_t xb_x(const rlb_model* m, int which) { return xb_logits(m) + (size_t)m->p.vocab_size * 8 + (size_t)which * m->p.dim * 8; }
+size_t xb_total(const rlb_model* m) { return xb_x(m, 2); }
 bool push_mode(const rlb_model* m) { return m->tp > 1 && m->tp_mode == 1; }
 
 // All-reduce of the partial sums of one projection when the NCCL mode is active.
@@ -190,6 +190,8 @@ int gemv_decode(rlb_model* m, rlb_dtype dtype, int prologue, int epilogue, const
         const int s = launch_gemv_stream(m->ctx, dtype, prologue, epilogue, a, m->scalars + 8, m->use_pdl && !m->profile);
         if (s != RLB_ERR_STATE) return s;
     }
+    if (a.ll_inbox != nullptr || a.n_outs > 0)
+        return rlb_fail(RLB_ERR_STATE, "the tensor-parallel push exchange needs the staged GEMV kernel, which does not take this shape (rows %d, K %d)", a.rows, a.K);
     return launch_gemv(m->ctx, dtype, prologue, epilogue, a);
 }
 
@@ -201,28 +203,28 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     const int32_t* pos = m->scalars + 1;
     const bool f16 = m->wdt == RLB_F16;
     const bool push = push_mode(m);
-    const int n_parts = push ? m->tp : 1;
-    // partial sums: local buffers, or (push mode) the inboxes every rank stores into
-    const float* parts_wo = push ? (const float*)(m->xbuf + xb_inbox_wo(m)) : m->part_wo;
-    const float* parts_w2 = push ? (const float*)(m->xbuf + xb_inbox_w2(m)) : m->part_w2;
-    float* logits = push ? (float*)(m->xbuf + xb_logits(m)) : m->logits;
+    const float* parts_wo = m->part_wo;
+    const float* parts_w2 = m->part_w2;
+    const uint32_t seq_stride = 2u * (uint32_t)m->p.n_layers + 1u;  // exchanges per decode step
 
-    // Producer side of an exchange step: store into every rank's inbox, count CTAs in at `flag_index`.
-    auto push_out = [&](GemvArgs& a, size_t inbox_off, int64_t offset, int flag_index) {
+    // Producer side of an exchange (push mode): tagged partial sums go into every rank's inbox.
+    auto push_out = [&](GemvArgs& a, size_t inbox_off, int64_t offset, uint32_t idx) {
         a.n_outs = m->tp;
         a.out_offset = offset;
-        for (int r = 0; r < m->tp; r++) {
-            a.outs[r] = (float*)(m->peer_xbuf[r] + inbox_off);
-            a.flags[r] = (unsigned long long*)(m->peer_xbuf[r] + xb_flag(m, flag_index));
-        }
+        a.out_seq_idx = idx + 1;
+        a.seq_stride = seq_stride;
+        a.epoch_ptr = m->scalars + 4;
+        for (int r = 0; r < m->tp; r++) a.ll_outs[r] = (uint2*)(m->peer_xbuf[r] + inbox_off);
     };
-    // Consumer side: wait until all tp * grid producer CTAs of this step have counted in.
-    auto push_wait = [&](GemvArgs& a, int flag_index, int producer_grid) {
-        a.wait_flag = (const unsigned long long*)(m->xbuf + xb_flag(m, flag_index));
-        a.wait_per_epoch = (unsigned long long)m->tp * (unsigned long long)producer_grid;
+    // Consumer side: poll this rank's inbox for exchange `idx`, publish the new residual in x buffer `which`.
+    auto push_in = [&](GemvArgs& a, size_t inbox_off, uint32_t idx, int which) {
+        a.ll_inbox = (const uint2*)(m->xbuf + inbox_off);
+        a.ll_x = (uint2*)(m->xbuf + xb_x(m, which));
+        a.n_parts = m->tp;
+        a.seq_idx = idx + 1;
+        a.seq_stride = seq_stride;
         a.epoch_ptr = m->scalars + 4;
     };
-    int grid_wo = 0, grid_w2 = 0, grid_head = 0;
 
     for (int l = 0; l < m->p.n_layers; l++) {
         const LayerW& W = m->L[l];
@@ -233,8 +235,8 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             a.W = W.wqkv; a.rows = 3 * m->nq; a.K = d; a.ldw = d;
             if (l == 0) { a.x_in = m->tok_emb; a.tok_ptr = tok; }
             else {
-                a.x_in = m->xb; a.parts = parts_w2; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
-                if (push) push_wait(a, 2 * (l - 1) + 1, grid_w2);
+                a.x_in = m->xb; a.parts = parts_w2; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
+                if (push) push_in(a, xb_inbox_w2(m), 2u * (l - 1) + 1u, 0);
             }
             a.x_out = m->xa; a.gain = W.attn_norm; a.eps = m->p.norm_eps;
             a.qbuf = m->qbuf; a.kcache = kc; a.vcache = vc; a.rope = m->rope; a.pos_ptr = pos;
@@ -254,9 +256,9 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             GemvArgs a;
             a.W = W.wo; a.rows = d; a.K = m->nq; a.ldw = m->nq; a.vec_in = m->obuf; a.out = m->part_wo;
             if (push) {
-                push_out(a, xb_inbox_wo(m), (int64_t)m->rank * d, 2 * l);
-                grid_wo = gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a);
-                if (grid_wo == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the wo projection");
+                push_out(a, xb_inbox_wo(m), (int64_t)m->rank * d, 2u * l);
+                if (gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a) == 0)
+                    return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the wo projection");
             }
             prof_mark(m, PC_WO);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
@@ -265,8 +267,8 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         {   // 4. residual + norm + w1/w3 + SiLU gate
             GemvArgs a;
             a.W = W.w1; a.W2 = W.w3; a.rows = m->F; a.K = d; a.ldw = d;
-            a.x_in = m->xa; a.parts = parts_wo; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
-            if (push) push_wait(a, 2 * l, grid_wo);
+            a.x_in = m->xa; a.parts = parts_wo; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
+            if (push) push_in(a, xb_inbox_wo(m), 2u * l, 1);
             a.x_out = m->xb; a.gain = W.ffn_norm; a.eps = m->p.norm_eps; a.out = m->gbuf;
             prof_mark(m, PC_W13);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_SWIGLU, a));
@@ -275,9 +277,9 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             GemvArgs a;
             a.W = W.w2; a.rows = d; a.K = m->F; a.ldw = m->F; a.vec_in = m->gbuf; a.out = m->part_w2;
             if (push) {
-                push_out(a, xb_inbox_w2(m), (int64_t)m->rank * d, 2 * l + 1);
-                grid_w2 = gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a);
-                if (grid_w2 == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the w2 projection");
+                push_out(a, xb_inbox_w2(m), (int64_t)m->rank * d, 2u * l + 1u);
+                if (gemv_stream_grid(ctx, m->wdt, PRO_COPY, EPI_F32, a) == 0)
+                    return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the w2 projection");
             }
             prof_mark(m, PC_W2);
             RLB_TRY(gemv_decode(m, m->wdt, PRO_COPY, EPI_F32, a));
@@ -287,14 +289,14 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     {   // final norm + f32 head (src/transformer.rs:378-381)
         GemvArgs a;
         a.W = m->output; a.rows = m->V; a.K = d; a.ldw = d;
-        a.x_in = m->xb; a.parts = parts_w2; a.n_parts = n_parts; a.part_stride = d; a.round_parts = f16;
-        if (push) push_wait(a, 2 * (m->p.n_layers - 1) + 1, grid_w2);
+        a.x_in = m->xb; a.parts = parts_w2; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
+        if (push) push_in(a, xb_inbox_w2(m), 2u * (m->p.n_layers - 1) + 1u, 0);
         a.gain = m->norm; a.eps = m->p.norm_eps;
         a.out = m->tp == 1 ? m->logits : m->logits_local;
         if (push) {
-            push_out(a, xb_logits(m), (int64_t)m->v0, 2 * m->p.n_layers);
-            grid_head = gemv_stream_grid(ctx, RLB_F32, PRO_NORM, EPI_F32, a);
-            if (grid_head == 0) return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the output head");
+            push_out(a, xb_logits(m), (int64_t)m->v0, 2u * m->p.n_layers);
+            if (gemv_stream_grid(ctx, RLB_F32, PRO_NORM, EPI_F32, a) == 0)
+                return rlb_fail(RLB_ERR_STATE, "push mode needs the staged GEMV kernel for the output head");
         }
         prof_mark(m, PC_HEAD);
         RLB_TRY(gemv_decode(m, RLB_F32, PRO_NORM, EPI_F32, a));
@@ -307,15 +309,17 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     sy.err = m->scalars + 8;
     if (push) {
         sy.epoch = m->scalars + 4;  // counts the decode steps run in push mode (starts at 1)
-        sy.wait_flag = (const unsigned long long*)(m->xbuf + xb_flag(m, 2 * m->p.n_layers));
-        sy.wait_per_epoch = (unsigned long long)m->tp * (unsigned long long)grid_head;
+        sy.ll_logits = (const uint2*)(m->xbuf + xb_logits(m));
+        sy.dense_out = m->logits;
+        sy.seq_idx = 2u * m->p.n_layers + 1u;
+        sy.seq_stride = seq_stride;
     }
     prof_mark(m, PC_ARGMAX);
     if (advance)
-        RLB_TRY(launch_argmax_advance(ctx, logits, m->p.vocab_size, m->scalars + 0, m->scalars + 1, m->scalars + 2, m->tokens_out,
+        RLB_TRY(launch_argmax_advance(ctx, m->logits, m->p.vocab_size, m->scalars + 0, m->scalars + 1, m->scalars + 2, m->tokens_out,
                                       m->tokens_cap, sy));
     else
-        RLB_TRY(launch_argmax(ctx, logits, m->p.vocab_size, m->scalars + 3, sy));
+        RLB_TRY(launch_argmax(ctx, m->logits, m->p.vocab_size, m->scalars + 3, sy));
     prof_mark(m, -1);
     return RLB_OK;
 }
@@ -823,8 +827,7 @@ int rlb_forward(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32_t n, i
     std::lock_guard<std::recursive_mutex> g(ctx->mu);
     RLB_CUDA(cudaSetDevice(ctx->device));
     RLB_TRY(forward_common(m, c, tokens, n, start_pos, false));
-    const float* logits_src = (n == 1 && push_mode(m)) ? (const float*)(m->xbuf + xb_logits(m)) : m->logits;
-    RLB_CUDA(cudaMemcpyAsync(m->h_logits, logits_src, (size_t)m->p.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    RLB_CUDA(cudaMemcpyAsync(m->h_logits, m->logits, (size_t)m->p.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaMemcpyAsync(m->h_scalars + 9, m->scalars + 8, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
     RLB_TRY(check_device_flag(m->h_scalars + 9));
