@@ -143,7 +143,8 @@ def test_device_greedy_loop_equals_host_loop(cuda_ctx):
         dev_tokens, ms = gpu.decode_greedy(first, len(prompt), 19, c)
         assert dev_tokens.tolist() == host_tokens[1:20]
         assert ms > 0.0
-        assert gpu.get_stat("kernels_per_step") == 5 * cfg["n_layers"] + 2
+        # one persistent kernel per token, or the chain of 5 L + 2 kernels where that one does not apply
+        assert gpu.get_stat("kernels_per_step") in (1, 5 * cfg["n_layers"] + 2)
 
 
 def test_cache_contents_clone_and_shift(cuda_ctx):
