@@ -370,16 +370,28 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     if (threadIdx.x == 0) ticket_sh = atomicAdd(a.counters + head, 1u);
     __syncthreads();
     if (ticket_sh != (unsigned)(active - 1)) return;
+    // last CTA of this head: merge the splits. Each split's weight exp(m_s - M) / L is computed
+    // once (by thread s) so that the per-column sums are plain independent loads.
     __threadfence();
+    __shared__ float sp_m[64], sp_w[64];
     const float* recs = a.scratch + (int64_t)head * a.n_split * (HD + 2);
+    if (threadIdx.x < active) {
+        sp_m[threadIdx.x] = __ldcg(recs + threadIdx.x * (HD + 2) + HD);
+        sp_w[threadIdx.x] = __ldcg(recs + threadIdx.x * (HD + 2) + HD + 1);
+    }
+    __syncthreads();
     float GM = -FLT_MAX;
-    for (int s = 0; s < active; s++) GM = fmaxf(GM, __ldcg(recs + s * (HD + 2) + HD));
+    for (int s = 0; s < active; s++) GM = fmaxf(GM, sp_m[s]);
     float GL = 0.f;
-    for (int s = 0; s < active; s++) GL += __ldcg(recs + s * (HD + 2) + HD + 1) * expf(__ldcg(recs + s * (HD + 2) + HD) - GM);
+    for (int s = 0; s < active; s++) GL += sp_w[s] * expf(sp_m[s] - GM);
+    __syncthreads();
+    if (threadIdx.x < active) sp_w[threadIdx.x] = expf(sp_m[threadIdx.x] - GM) / GL;
+    __syncthreads();
     if (c < HD) {
         float go = 0.f;
-        for (int s = 0; s < active; s++) go += __ldcg(recs + s * (HD + 2) + c) * expf(__ldcg(recs + s * (HD + 2) + HD) - GM);
-        out[c] = cast_out<CT>(go / GL);
+#pragma unroll 4
+        for (int s = 0; s < active; s++) go += __ldcg(recs + s * (HD + 2) + c) * sp_w[s];
+        out[c] = cast_out<CT>(go);
     }
     if (threadIdx.x == 0) a.counters[head] = 0;  // ready for the next launch
 }

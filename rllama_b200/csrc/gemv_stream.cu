@@ -322,20 +322,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                 for (int q = 1; q < RLB_MAX_TP; q++)
                     if (q < a.n_parts) sum += part[q];  // fixed rank order: identical on every rank
                 if (a.round_parts) sum = round_f16(sum);
-                const float v = xin[i] + sum;
-                if (a.x_out) a.x_out[i] = v;
-                ll_store(a.ll_x + i, v, seq);
+                a.x_out[i] = xin[i] + sum;
             }
-            for (int base = tid; base < K; base += 8 * kConsumers) {
-                float v8[8];
-                const int cnt = min(8, (K - base + kConsumers - 1) / kConsumers);
-                ll_gather<8>(a.ll_x + base, (size_t)kConsumers, cnt, seq, v8, dead, cfg.err);
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    if (j < cnt) {
-                        tmp[base + j * kConsumers] = v8[j];
-                        ss = fmaf(v8[j], v8[j], ss);
-                    }
+            // Publish the slice with plain stores, a device-scope fence and one count per CTA; the
+            // other CTAs poll that single counter (thousands of threads polling entries would
+            // compete with the stores they wait for), then read the row through L2.
+            __threadfence();
+            consumer_sync();
+            if (tid == 0) {
+                atomicAdd(a.xready, 1u);
+                const unsigned int target = (unsigned int)(*a.epoch_ptr) * gridDim.x;
+                bool ok = false;
+                for (uint32_t it = 0; it < (1u << 20) && !*dead; it++) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.xready) : "memory");
+                    if (v >= target) { ok = true; break; }
+                    __nanosleep(40);
+                }
+                if (!ok) { *dead = 1; atomicExch(cfg.err, 2); }
+            }
+            consumer_sync();
+            for (int i = tid * 4; i < K; i += kConsumers * 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(a.x_out + i));
+                *reinterpret_cast<float4*>(tmp + i) = v;
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
             }
         } else {
             for (int i = tid * 4; i < K; i += kConsumers * 4) {

@@ -111,7 +111,7 @@ struct GemvArgs {
     int n_outs = 0;                  // 0: write `out` only
     int64_t out_offset = 0;
     const uint2* ll_inbox = nullptr; // PRO_NORM consumer: this rank's inbox, n_parts x K entries
-    uint2* ll_x = nullptr;           // PRO_NORM consumer: K entries where slice owners publish the new residual
+    unsigned int* xready = nullptr;  // PRO_NORM consumer: counts the CTAs that have published their slice of x_out
     uint32_t seq_idx = 0, seq_stride = 0, out_seq_idx = 0;
     const int32_t* epoch_ptr = nullptr;
     // EPI_QKV

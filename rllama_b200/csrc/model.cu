@@ -181,7 +181,8 @@ size_t xb_inbox_wo(const rlb_model*) { return 0; }
 size_t xb_inbox_w2(const rlb_model* m) { return (size_t)m->tp * m->p.dim * 8; }
 size_t xb_logits(const rlb_model* m) { return 2 * (size_t)m->tp * m->p.dim * 8; }
 size_t xb_x(const rlb_model* m, int which) { return xb_logits(m) + (size_t)m->p.vocab_size * 8 + (size_t)which * m->p.dim * 8; }
-size_t xb_total(const rlb_model* m) { return xb_x(m, 2); }
+size_t xb_ready(const rlb_model* m, int idx) { return ((xb_x(m, 2) + 127) & ~(size_t)127) + (size_t)idx * 128; }  // one line per exchange
+size_t xb_total(const rlb_model* m) { return xb_ready(m, 2 * m->p.n_layers + 2); }
 bool push_mode(const rlb_model* m) { return m->tp > 1 && m->tp_mode == 1; }
 
 // All-reduce of the partial sums of one projection when the NCCL mode is active.
@@ -226,7 +227,7 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     // Consumer side: poll this rank's inbox for exchange `idx`, publish the new residual in x buffer `which`.
     auto push_in = [&](GemvArgs& a, size_t inbox_off, uint32_t idx, int which) {
         a.ll_inbox = (const uint2*)(m->xbuf + inbox_off);
-        a.ll_x = (uint2*)(m->xbuf + xb_x(m, which));
+        a.xready = (unsigned int*)(m->xbuf + xb_ready(m, (int)idx));
         a.n_parts = m->tp;
         a.seq_idx = idx + 1;
         a.seq_stride = seq_stride;
@@ -298,6 +299,7 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         a.W = m->output; a.rows = m->V; a.K = d; a.ldw = d;
         a.x_in = m->xb; a.parts = parts_w2; a.n_parts = 1; a.part_stride = d; a.round_parts = f16;
         if (push) push_in(a, xb_inbox_w2(m), 2u * (m->p.n_layers - 1) + 1u, 0);
+        a.x_out = m->xa;  // the final residual row (the push exchange publishes it there)
         a.gain = m->norm; a.eps = m->p.norm_eps;
         a.out = m->tp == 1 ? m->logits : m->logits_local;
         if (push) {
@@ -638,11 +640,11 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
     A((void**)&m->scalars, 16 * sizeof(int32_t));
     m->tokens_cap = p->max_seq_len;
     A((void**)&m->tokens_out, (size_t)m->tokens_cap * sizeof(int32_t));
-    // split attention over positions so that roughly two CTAs per SM are busy
-    int ns = (2 * ctx->sm_count + m->nh - 1) / m->nh;
+    // split attention over positions (64 per CTA at least) so that about three small CTAs per SM are busy
+    int ns = (3 * ctx->sm_count + m->nh - 1) / m->nh;
     const int max_ns = (p->max_seq_len + 63) / 64;
     if (ns > max_ns) ns = max_ns;
-    if (ns > 16) ns = 16;
+    if (ns > 32) ns = 32;
     if (ns < 1) ns = 1;
     if (const char* e = getenv("RLB_ATTN_SPLIT")) { int v = atoi(e); if (v >= 1 && v <= 64) ns = v; }
     m->n_split = ns;
