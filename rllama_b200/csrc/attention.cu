@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefil
     float* o_sh = q_sh + hd;
     float* accbuf = o_sh + hd;
     float* sc = accbuf + kThreads * CVec<CT>::N;
-    for (int c = threadIdx.x; c < hd; c += kThreads) q_sh[c] = a.q[(int64_t)i * a.heads * hd + head * hd + c];
+    for (int c = threadIdx.x; c < hd; c += kThreads) q_sh[c] = a.q[(int64_t)i * a.q_ld + head * hd + c];
     __syncthreads();
     const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * hd;
     const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * hd;

@@ -88,6 +88,7 @@ int rlb_ctx_destroy(rlb_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->op_scratch) cudaFree(ctx->op_scratch);
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
     if (ctx->h_err) cudaFreeHost(ctx->h_err);
     cudaStreamDestroy(ctx->stream);
     delete ctx;

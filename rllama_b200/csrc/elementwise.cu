@@ -45,14 +45,14 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, int dim, const 
 
 // apply_rotary_emb (src/transformer.rs:823-856) + the cache write loop (:751-761).
 template <typename CT>
-__global__ void rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int start_pos,
-                                   int heads, int hd, int max_seq, const float* __restrict__ rope, CT* __restrict__ kcache,
-                                   CT* __restrict__ vcache) {
+__global__ void rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int64_t ld,
+                                   int start_pos, int heads, int hd, int max_seq, const float* __restrict__ rope,
+                                   CT* __restrict__ kcache, CT* __restrict__ vcache) {
     const int i = blockIdx.x, pos = start_pos + i, nq = heads * hd;
     for (int p = threadIdx.x; p < nq / 2; p += blockDim.x) {
         const int head = (2 * p) / hd, c = 2 * p - head * hd;
         const float fr = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2], fi = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2 + 1];
-        const int64_t idx = (int64_t)i * nq + 2 * p;
+        const int64_t idx = (int64_t)i * ld + 2 * p;
         const float qr = q[idx], qi = q[idx + 1], kr = k[idx], ki = k[idx + 1];
         q[idx] = __fsub_rn(__fmul_rn(qr, fr), __fmul_rn(qi, fi));
         q[idx + 1] = __fadd_rn(__fmul_rn(qr, fi), __fmul_rn(qi, fr));
@@ -66,11 +66,14 @@ __global__ void rope_append_kernel(float* __restrict__ q, const float* __restric
 
 // silu_cpu + hadamard_product_cpu (src/tensor.rs:822-832, :722-734) and the cast before w2.
 template <typename OT>
-__global__ void swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t count, OT* __restrict__ out) {
+__global__ void swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t rows, int64_t cols,
+                              OT* __restrict__ out) {
+    const int64_t count = rows * cols;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
-        const float v = a1[i];
+        const int64_t r = i / cols, c = i - r * cols;
+        const float v = a1[r * ld + c];
         const float s = v / (1.0f + expf(-v));
-        out[i] = cast_to<OT>(__fmul_rn(s, a3[i]));
+        out[i] = cast_to<OT>(__fmul_rn(s, a3[r * ld + c]));
     }
 }
 
@@ -259,20 +262,22 @@ int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const floa
     return RLB_OK;
 }
 
-int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int n, int start_pos, int heads, int hd, int max_seq,
-                       const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache) {
+int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int64_t ld, int n, int start_pos, int heads, int hd,
+                       int max_seq, const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache) {
     if (cache_dtype == RLB_F16)
-        rope_append_kernel<__half><<<n, 256, 0, ctx->stream>>>(q, k, v, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
+        rope_append_kernel<__half><<<n, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
     else
-        rope_append_kernel<float><<<n, 256, 0, ctx->stream>>>(q, k, v, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
+        rope_append_kernel<float><<<n, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
 }
 
-int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t count, rlb_dtype out_dtype, void* out) {
-    if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, count, (__half*)out);
-    else swiglu_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, count, (float*)out);
+int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t ld, int64_t rows, int64_t cols, rlb_dtype out_dtype,
+                       void* out) {
+    const int64_t count = rows * cols;
+    if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (__half*)out);
+    else swiglu_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (float*)out);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;

@@ -5,7 +5,9 @@
 //
 // One CTA computes a 128 (weight rows) x BN (tokens) tile:
 //  * operands arrive by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the
-//    tensor) into a 4-stage shared-memory ring; one thread issues the loads;
+//    tensor) into a shared-memory ring of 4 to 8 stages (192 KB); one thread issues the loads;
+//  * when the output has few tiles (short prompts, wo / w2) K is split over blockIdx.z and a
+//    second kernel adds the partial tiles in a fixed order;
 //  * one thread issues tcgen05.mma (kind::f16, M 128, N BN, K 16 per instruction, four per
 //    64-column stage) with the accumulator in tensor memory; tcgen05.commit releases a ring
 //    slot when the MMAs that read it have finished;
@@ -26,7 +28,10 @@ namespace {
 
 constexpr int BM = 128;       // weight rows per tile (MMA M)
 constexpr int BK = 64;        // K columns per stage: 128 bytes of f16 = one swizzle span
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;
+constexpr int kRingBytes = 192 * 1024;  // shared memory given to the operand ring
+// stages that fit the ring for a token tile of BN rows (a weight tile is always 128 x 64 f16)
+constexpr int stages_for(int bn) { return (kRingBytes / (BM * BK * 2 + bn * BK * 2)) < kMaxStages ? (kRingBytes / (BM * BK * 2 + bn * BK * 2)) : kMaxStages; }
 constexpr int kTcThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr uint32_t kWaitLimit = 1u << 22;
 
@@ -88,10 +93,14 @@ template <typename OT> __device__ __forceinline__ OT out_cast(float v);
 template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return __float2half_rn(v); }
 
+// blockIdx.z selects a K range (split-K): with more than one split every split stores its f32
+// partial tile into its own [n][ldc] slab of C (slab stride `split_stride` elements) and a second
+// kernel adds the slabs in a fixed order, so the result does not depend on timing.
 template <int BN, typename OT>
 __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                              const __grid_constant__ CUtensorMap tm_x, OT* __restrict__ C, int64_t ldc,
-                                                             int n, int Mrows, int K, int round_out, int* err) {
+                                                             int n, int Mrows, int K, int round_out, int64_t split_stride, int* err) {
+    constexpr int kStages = stages_for(BN);
     constexpr uint32_t A_BYTES = BM * BK * 2;
     constexpr uint32_t B_BYTES = BN * BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -109,7 +118,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM;  // first weight row of the tile
     const int n0 = blockIdx.y * BN;  // first token of the tile
-    const int nkb = (K + BK - 1) / BK;
+    const int nkb_total = (K + BK - 1) / BK;
+    const int per_split = (nkb_total + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int kb_first = (int)blockIdx.z * per_split;
+    const int nkb = max(0, min(nkb_total, kb_first + per_split) - kb_first);  // k-blocks of this split
+    C += (int64_t)blockIdx.z * split_stride;
 
     if (threadIdx.x == 0) {
         dead_flag = 0;
@@ -139,8 +152,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
             unsigned char* a_s = tiles + (size_t)s * STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a_s, &tm_w, kb * BK, m0, &full_bar[s]);
-            tma_load_2d(a_s + A_BYTES, &tm_x, kb * BK, n0, &full_bar[s]);
+            tma_load_2d(a_s, &tm_w, (kb_first + kb) * BK, m0, &full_bar[s]);
+            tma_load_2d(a_s + A_BYTES, &tm_x, (kb_first + kb) * BK, n0, &full_bar[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
                 for (int j = 0; j < 16; j++) {
                     const int token = n0 + c0 + j;
                     if (token < n && row < Mrows) {
-                        float v = __uint_as_float(r[j]);
+                        float v = nkb > 0 ? __uint_as_float(r[j]) : 0.f;
                         if (round_out) v = __half2float(__float2half_rn(v));
                         C[(int64_t)token * ldc + row] = out_cast<OT>(v);
                     }
@@ -200,6 +213,20 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// Second pass of split-K: out[i][j] = cast(round?(sum over slabs in slab order)).
+template <typename OT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int64_t slab_stride, int splits, int64_t ld_part, OT* __restrict__ out,
+                                     int64_t ldc, int n, int M, int round_out) {
+    const int64_t total = (int64_t)n * M;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / M, c = i - r * M;
+        float v = 0.f;
+        for (int z = 0; z < splits; z++) v += part[z * slab_stride + r * ld_part + c];
+        if (round_out) v = __half2float(__float2half_rn(v));
+        out[r * ldc + c] = out_cast<OT>(v);
     }
 }
 
@@ -231,15 +258,54 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int
 
 template <int BN, typename OT>
 int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, OT* C, int64_t ldc, int n, int M, int K, int round_out, int* err) {
-    auto kern = gemm_tc_kernel<BN, OT>;
-    const size_t smem = (size_t)kStages * (BM * BK * 2 + BN * BK * 2) + 1024;
+    const size_t smem = (size_t)stages_for(BN) * (BM * BK * 2 + BN * BK * 2) + 1024;
+    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN, 1);
+    // few tiles: split K so that most SMs stream weights
+    const int tiles = (int)(grid.x * grid.y), nkb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (tiles * 5 < ctx->sm_count * 3) {
+        splits = (ctx->sm_count + tiles - 1) / tiles;
+        if (splits > 8) splits = 8;
+        while (splits > 1 && nkb / splits < 8) splits--;
+    }
+    if (splits == 1) {
+        auto kern = gemm_tc_kernel<BN, OT>;
+        static bool set = false;
+        if (!set) {
+            RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set = true;
+        }
+        kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, C, ldc, n, M, K, round_out, 0, err);
+        RLB_LAUNCH_CHECK();
+        count_launch(ctx);
+        return RLB_OK;
+    }
+    // slabs of f32 partial tiles in the context's scratch
+    const size_t need = (size_t)splits * n * M * sizeof(float);
+    if (need > ctx->gemm_scratch_bytes) {
+        RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+        ctx->gemm_scratch = nullptr;
+        ctx->gemm_scratch_bytes = 0;
+        cudaError_t e = cudaMalloc(&ctx->gemm_scratch, need);
+        if (e != cudaSuccess) return rlb_fail(RLB_ERR_OOM, "split-K scratch (%zu bytes): %s", need, cudaGetErrorString(e));
+        ctx->gemm_scratch_bytes = need;
+    }
+    float* part = static_cast<float*>(ctx->gemm_scratch);
+    auto kern = gemm_tc_kernel<BN, float>;
     static bool set = false;
     if (!set) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN);
-    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, C, ldc, n, M, K, round_out, err);
+    grid.z = splits;
+    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, part, (int64_t)M, n, M, K, 0, (int64_t)n * M, err);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    const int64_t total = (int64_t)n * M;
+    int rg = (int)((total + 255) / 256);
+    if (rg > ctx->sm_count * 8) rg = ctx->sm_count * 8;
+    splitk_reduce_kernel<OT><<<rg, 256, 0, ctx->stream>>>(part, (int64_t)n * M, splits, (int64_t)M, C, ldc, n, M, round_out);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;

@@ -44,6 +44,8 @@ struct rlb_ctx {
     uint64_t launches = 0;  // kernels launched by this library on this context
     void* op_scratch = nullptr;  // scratch of the standalone attention op, grown on demand
     size_t op_scratch_bytes = 0;
+    void* gemm_scratch = nullptr;  // split-K partial tiles of the tensor-core GEMM, grown on demand
+    size_t gemm_scratch_bytes = 0;
     // error word of the op-level kernels: mapped pinned host memory, so the host reads it after a
     // synchronisation without a copy (raised when a bounded device-side wait ran out)
     int* h_err = nullptr;
@@ -214,7 +216,8 @@ int attention_check(const rlb_tensor* out, const rlb_tensor* q, const rlb_tensor
 size_t attn_decode_scratch_floats(int heads, int hd, int n_split);
 
 struct AttnPrefillArgs {
-    const float* q = nullptr;      // [n][heads*hd] f32 rotated
+    const float* q = nullptr;      // n rows of heads*hd f32 (rotated), row stride q_ld
+    int64_t q_ld = 0;
     const void* kcache = nullptr;
     const void* vcache = nullptr;
     void* out = nullptr;           // [n][heads*hd] weight dtype
@@ -229,11 +232,13 @@ int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, in
 // a[n][dim] (weight dtype) = cast(rmsnorm(x) * gain)
 int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype,
                         void* out);
-// q,k,v: [n][nq] f32 GEMM outputs (already rounded when f16). Rotates q in place, writes K (rotated) and V to the cache.
-int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int n, int start_pos, int heads, int hd,
-                       int max_seq, const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache);
-// g[n][F] (weight dtype) = cast(silu(a1) * a3)
-int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t count, rlb_dtype out_dtype, void* out);
+// q,k,v: n rows of nq f32 GEMM outputs (already rounded when f16), row stride ld. Rotates q in place, writes K (rotated)
+// and V to the cache.
+int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int64_t ld, int n, int start_pos, int heads,
+                       int hd, int max_seq, const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache);
+// g[rows][cols] (weight dtype, dense) = cast(silu(a1) * a3); a1, a3 have row stride ld
+int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t ld, int64_t rows, int64_t cols, rlb_dtype out_dtype,
+                       void* out);
 // x[i] += round_f16?(y[i])
 int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int round_f16);
 // Optional wait of the arg-max kernels for pushed logits (tensor-parallel push mode), and the

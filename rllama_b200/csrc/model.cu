@@ -492,8 +492,7 @@ int ensure_prefill_buffers(rlb_model* m, int n) {
     RLB_TRY(dev_alloc_t(&m->pf_qkv, N * 3 * m->nq));
     RLB_TRY(dev_alloc(&m->pf_o, N * m->nq * m->wsz));
     RLB_TRY(dev_alloc_t(&m->pf_p, N * d));
-    RLB_TRY(dev_alloc_t(&m->pf_g1, N * m->F));
-    RLB_TRY(dev_alloc_t(&m->pf_g3, N * m->F));
+    RLB_TRY(dev_alloc_t(&m->pf_g1, N * 2 * m->F));
     RLB_TRY(dev_alloc(&m->pf_g, N * m->F * m->wsz));
     RLB_TRY(dev_alloc_t(&m->pf_last, d));
     m->pf_cap = n;
@@ -512,23 +511,21 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
         char* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.attn_norm, m->p.norm_eps, m->wdt, m->pf_a));
-        // q, k, v as three GEMMs into contiguous [n][nq] blocks
-        for (int s = 0; s < 3; s++)
-            RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, (char*)W.wqkv + (size_t)s * nq * d * m->wsz, d,
-                                   m->pf_qkv + (size_t)s * n * nq, nq, n, nq, d, f16, m->scalars + 8));
-        RLB_TRY(launch_rope_append(ctx, m->pf_qkv, m->pf_qkv + (size_t)n * nq, m->pf_qkv + (size_t)2 * n * nq, n, start_pos, m->nh,
-                                   m->hd, m->p.max_seq_len, m->rope, m->wdt, kc, vc));
+        // q, k and v in one GEMM: row i of the result is [q_i | k_i | v_i]
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.wqkv, d, m->pf_qkv, 3 * nq, n, 3 * nq, d, f16, m->scalars + 8));
+        RLB_TRY(launch_rope_append(ctx, m->pf_qkv, m->pf_qkv + nq, m->pf_qkv + 2 * nq, 3 * nq, n, start_pos, m->nh, m->hd,
+                                   m->p.max_seq_len, m->rope, m->wdt, kc, vc));
         AttnPrefillArgs aa;
-        aa.q = m->pf_qkv; aa.kcache = kc; aa.vcache = vc; aa.out = m->pf_o; aa.n = n; aa.start_pos = start_pos;
+        aa.q = m->pf_qkv; aa.q_ld = 3 * nq; aa.kcache = kc; aa.vcache = vc; aa.out = m->pf_o; aa.n = n; aa.start_pos = start_pos;
         aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len;
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, F, n, F, d, f16, m->scalars + 8));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w3, d, m->pf_g3, F, n, F, d, f16, m->scalars + 8));
-        RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g3, (int64_t)n * F, m->wdt, m->pf_g));
+        // w1 and w3 (stored back to back) in one GEMM: row i of the result is [w1 x_i | w3 x_i]
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, 2 * F, n, 2 * F, d, f16, m->scalars + 8));
+        RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g1 + F, 2 * F, n, F, m->wdt, m->pf_g));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj, m->scalars + 8));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
@@ -623,8 +620,8 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
     for (auto& W : m->L) {
         A(&W.wqkv, (size_t)3 * m->nq * d * m->wsz);
         A(&W.wo, d * m->nq * m->wsz);
-        A(&W.w1, (size_t)m->F * d * m->wsz);
-        A(&W.w3, (size_t)m->F * d * m->wsz);
+        A(&W.w1, (size_t)2 * m->F * d * m->wsz);  // w1 and w3 back to back: one GEMM serves both at prefill
+        if (W.w1) W.w3 = (char*)W.w1 + (size_t)m->F * d * m->wsz;
         A(&W.w2, d * m->F * m->wsz);
         A((void**)&W.attn_norm, d * 4);
         A((void**)&W.ffn_norm, d * 4);
@@ -778,7 +775,7 @@ int rlb_model_free(rlb_model* m) {
                     m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g3, m->pf_g, m->pf_last};
     for (void* p : ptrs) if (p) cudaFree(p);
     for (auto& W : m->L) {
-        void* lp[] = {W.wqkv, W.wo, W.w1, W.w3, W.w2, W.attn_norm, W.ffn_norm};
+        void* lp[] = {W.wqkv, W.wo, W.w1, W.w2, W.attn_norm, W.ffn_norm};
         for (void* p : lp) if (p) cudaFree(p);
     }
     if (m->h_scalars) cudaFreeHost(m->h_scalars);
