@@ -183,7 +183,8 @@ int rlb_tp_nccl_unique_id(void* id128);
 int rlb_tp_nccl_init(rlb_model* m, const void* id128);
 int rlb_tp_peer_export(rlb_model* m, void* handle128);
 int rlb_tp_peer_import(rlb_model* m, const void* handles, int32_t n_handles);
-/* mode: 0 = NCCL all-reduce, 1 = fused one-shot push over peer memory.                 */
+/* mode: 0 = NCCL all-reduce / all-gather, 1 = fused push exchange over peer memory (needs
+ * rlb_tp_peer_import; prefill keeps using NCCL). Every rank must switch at the same step. */
 int rlb_tp_set_mode(rlb_model* m, int32_t mode);
 
 /* Transformer::make_caches (src/transformer.rs:328-341).                              */
@@ -215,9 +216,11 @@ int rlb_forward_greedy(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32
 int rlb_decode_greedy(rlb_model* m, rlb_caches* c, int32_t first_token, int32_t start_pos, int32_t n_steps,
                       int32_t* tokens_out, float* elapsed_ms);
 
-/* Device time in ms of the dominant decode kernels during the last rlb_decode_greedy,
- * when profiling was switched on with rlb_model_set_profiling(m, 1): events bracket
- * every kernel class. names_out receives a NUL-separated list. (inspection only)       */
+/* Tuning and inspection. Options: "graph" (replay the decode step as a CUDA graph, default 1),
+ * "stream_gemv" (bulk-copy staged GEMV kernels, default 1), "pdl" (programmatic dependent launch,
+ * default 1), "persistent" (one cooperative kernel per token, default 0), "profile" (time every
+ * kernel class of the decode step). Statistics: "kernels_per_step", "attn_split", "local_heads",
+ * "first_head", "local_ffn", "local_vocab", "prof_steps", "prof_ms_<qkv|attn|wo|w13|w2|head|argmax|comm>". */
 int rlb_model_set_option(rlb_model* m, const char* name, int64_t value);
 int rlb_model_get_stat(rlb_model* m, const char* name, double* value);
 

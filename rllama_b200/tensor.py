@@ -3,6 +3,7 @@
 the way ``src/tensor.rs``'s ``#[cfg(feature = "opencl")]`` tests use the OpenCL backend.
 """
 import ctypes
+import sys
 
 import numpy as np
 
@@ -110,7 +111,9 @@ class CudaTensor:
             self._h = ctypes.c_void_p()
 
     def __del__(self):
+        # at interpreter shutdown the CUDA runtime may already be gone: leave the memory to process exit
         try:
-            self.free()
+            if sys is not None and not sys.is_finalizing():
+                self.free()
         except Exception:
             pass

@@ -4,6 +4,7 @@
 reference so that tests read like its own.
 """
 import ctypes
+import sys
 
 import numpy as np
 
@@ -148,8 +149,10 @@ class Transformer:
             self._h = ctypes.c_void_p()
 
     def __del__(self):
+        # at interpreter shutdown the CUDA runtime may already be gone: leave the memory to process exit
         try:
-            self.free()
+            if sys is not None and not sys.is_finalizing():
+                self.free()
         except Exception:
             pass
 
@@ -185,7 +188,9 @@ class TransformerCaches:
             self._h = ctypes.c_void_p()
 
     def __del__(self):
+        # at interpreter shutdown the CUDA runtime may already be gone: leave the memory to process exit
         try:
-            self.free()
+            if sys is not None and not sys.is_finalizing():
+                self.free()
         except Exception:
             pass
