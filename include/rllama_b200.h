@@ -216,6 +216,34 @@ int rlb_forward_greedy(rlb_model* m, rlb_caches* c, const int32_t* tokens, int32
 int rlb_decode_greedy(rlb_model* m, rlb_caches* c, int32_t first_token, int32_t start_pos, int32_t n_steps,
                       int32_t* tokens_out, float* elapsed_ms);
 
+/* ------------------------------------------------------------------------------------
+ * Checkpoint loading (host side): the unzipped Meta LLaMA layout rllama reads.
+ * ---------------------------------------------------------------------------------- */
+typedef struct rlb_data_source rlb_data_source;  /* `DataSource::LLaMASource` (src/data_source.rs:22-30) */
+
+/* DataSource::from_llama_source (src/data_source.rs:166-196): unpickles
+ * <model_path>/consolidated.NN/data.pkl for NN = 00, 01, ... until one is missing.      */
+int rlb_data_source_open(const char* model_path, rlb_data_source** out);
+int rlb_data_source_free(rlb_data_source* ds);
+int rlb_data_source_shards(rlb_data_source* ds, int32_t* n_shards);
+/* Shape of a named tensor after concatenating its shards. direction: 0 = along rows,
+ * 1 = along columns (FromPiecesDirection, src/tensor.rs:2340-2343), 2 = first shard only
+ * (Tensor::from_unpickled_pieces1, src/tensor.rs:309-329).                               */
+int rlb_data_source_tensor_shape(rlb_data_source* ds, const char* name, int32_t direction, int64_t* rows, int64_t* cols);
+/* TensorBuilder::load_from_pieces (src/tensor.rs:2388-2545): reads the f16 rows of every
+ * shard from consolidated.NN/data/<key> into out[rows][cols] (dense, f16 bit patterns).  */
+int rlb_data_source_read_f16(rlb_data_source* ds, const char* name, int32_t direction, uint16_t* out, int64_t rows, int64_t cols);
+/* ModelParams from params.json (src/model_params.rs:4-14, src/rllama_main.rs:201-241):
+ * fills dim, n_heads, n_layers, norm_eps, vocab_size (HF aliases accepted); the other
+ * fields of *out are left untouched.                                                     */
+int rlb_model_params_from_json(const char* path, rlb_model_params* out);
+/* Transformer::from_unpickled (src/transformer.rs:242-326) with Embedding::from_unpickled
+ * (src/embedding.rs:13-48): creates the model and loads every tensor by its Meta name.
+ * ffn_dim and vocab_size of *params are ignored: they come from the w1 and embedding
+ * tensors, as in the reference. Every tensor-parallel rank reads the whole checkpoint and
+ * keeps its slice.                                                                       */
+int rlb_model_from_llama_source(rlb_ctx* ctx, rlb_data_source* ds, const rlb_model_params* params, rlb_model** out);
+
 /* Tuning and inspection. Options: "graph" (replay the decode step as a CUDA graph, default 1),
  * "stream_gemv" (bulk-copy staged GEMV kernels, default 1), "pdl" (programmatic dependent launch,
  * default 1), "persistent" (one cooperative kernel per token, default 0), "profile" (time every

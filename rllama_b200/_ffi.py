@@ -24,6 +24,8 @@ EXPORTS = [
     "rlb_caches_create", "rlb_caches_true_clone", "rlb_caches_shift_left", "rlb_caches_free", "rlb_caches_read",
     "rlb_forward", "rlb_forward_greedy", "rlb_decode_greedy",
     "rlb_model_set_option", "rlb_model_get_stat",
+    "rlb_data_source_open", "rlb_data_source_free", "rlb_data_source_shards", "rlb_data_source_tensor_shape",
+    "rlb_data_source_read_f16", "rlb_model_params_from_json", "rlb_model_from_llama_source",
 ]
 
 
@@ -82,6 +84,12 @@ def lib():
         "rlb_decode_greedy": [vp, vp, i32, i32, i32, vp, P(ctypes.c_float)],
         "rlb_model_set_option": [vp, ctypes.c_char_p, i64],
         "rlb_model_get_stat": [vp, ctypes.c_char_p, P(ctypes.c_double)],
+        "rlb_data_source_open": [ctypes.c_char_p, P(vp)], "rlb_data_source_free": [vp],
+        "rlb_data_source_shards": [vp, P(i32)],
+        "rlb_data_source_tensor_shape": [vp, ctypes.c_char_p, i32, P(i64), P(i64)],
+        "rlb_data_source_read_f16": [vp, ctypes.c_char_p, i32, vp, i64, i64],
+        "rlb_model_params_from_json": [ctypes.c_char_p, P(ModelParams)],
+        "rlb_model_from_llama_source": [vp, vp, P(ModelParams), P(vp)],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

@@ -57,6 +57,24 @@ class Transformer:
         check(_ffi.lib().rlb_model_create(self.cl._h, ctypes.byref(p), ctypes.byref(self._h)))
 
     # -- construction -------------------------------------------------------------------
+    @classmethod
+    def from_unpickled(cls, dim, n_layers, n_heads, max_seq_len, eps, data_settings, data_source, tp_rank=0, tp_size=1):
+        """``Transformer::from_unpickled(emb, dim, n_layers, n_heads, max_seq_len, eps, data_settings,
+        data_source)``: loads every tensor of a LLaMA checkpoint by its Meta name (the embedding
+        table included; FFN width and vocabulary size come from the tensors)."""
+        self = cls.__new__(cls)
+        ds = data_settings or DataSettings()
+        self.cl = ds.cl or Cuda(verbose=False, nth_device=0)
+        p = ModelParams(dim, n_layers, n_heads, 0, 0, max_seq_len, float(eps), int(ds._force_f16), int(tp_rank), int(tp_size))
+        self._h = ctypes.c_void_p()
+        check(_ffi.lib().rlb_model_from_llama_source(self.cl._h, data_source._h, ctypes.byref(p), ctypes.byref(self._h)))
+        self.dim, self.n_layers, self.n_heads = dim, n_layers, n_heads
+        self.ffn_dim = data_source.tensor_shape("layers.0.feed_forward.w1.weight", 0)[0]
+        self.vocab_size = data_source.tensor_shape("tok_embeddings.weight", 1)[0]
+        self.max_seq_len, self.eps, self.force_f16 = max_seq_len, eps, ds._force_f16
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        return self
+
     def set_tensor(self, kind, layer, array):
         """One whole checkpoint tensor (numpy f16/f32, or a torch tensor on any device)."""
         k = TENSOR_KINDS[kind] if isinstance(kind, str) else int(kind)
