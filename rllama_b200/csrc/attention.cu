@@ -15,6 +15,7 @@
 
 #include <cfloat>
 #include <cstdlib>
+#include <cstdio>
 
 namespace {
 
@@ -268,7 +269,24 @@ __host__ __device__ inline int fast_chunk(int T, int ns) {
     return chunk;
 }
 
-template <typename CT, int HD>
+// Distributed shared memory of a thread-block cluster: address of `addr` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map(const void* addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(addr)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// CL = false: the splits of a head meet through records in global memory and a ticket counter; the
+// CTA that draws the last ticket merges them. CL = true: the n_split (<= 8) CTAs of a head form a
+// thread-block cluster, send their partial result into the shared memory of the cluster's first
+// CTA and meet at the cluster barrier: no global round trips on the way to the merged row.
+template <typename CT, int HD, bool CL>
 __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDecodeArgs a) {
     constexpr int DPL = HD / 32;
     constexpr int PB = 8;  // positions per warp per batch
@@ -277,16 +295,29 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     __shared__ float w_o[kWarps][HD];
     __shared__ unsigned int ticket_sh;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Before waiting for the projection kernel: the position (only the last kernel of a decode step
+    // changes it) and the cache rows of earlier positions (written by earlier steps) are already
+    // final, so the first batch of K and V rows is requested now and its latency overlaps the wait.
     const int head = blockIdx.x, split = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int T = *a.pos_ptr + 1;
     const int chunk = fast_chunk(T, a.n_split);
     const int active = (T + chunk - 1) / chunk;  // splits with at least one position
-    if (split >= active) return;
+    const bool work = split < active;
+    if (!CL && !work) return;  // (in a cluster every CTA goes on to the barrier; its loops below are empty)
     const int t0 = split * chunk, t1 = min(T, t0 + chunk);
     const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * HD + lane * DPL;
     const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * HD + lane * DPL;
+    RV kv[PB], vv[PB];
+#pragma unroll
+    for (int j = 0; j < PB; j++) {
+        const int t = t0 + warp + j * kWarps;
+        if (t < t1 && t < T - 1) {
+            kv[j] = *reinterpret_cast<const RV*>(kbase + (int64_t)t * HD);
+            vv[j] = *reinterpret_cast<const RV*>(vbase + (int64_t)t * HD);
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float q[DPL];
 #pragma unroll
     for (int d = 0; d < DPL; d++) q[d] = a.q[head * HD + lane * DPL + d];
@@ -296,11 +327,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     for (int d = 0; d < DPL; d++) acc[d] = 0.f;
 
     for (int tb = t0 + warp; tb < t1; tb += kWarps * PB) {
-        RV kv[PB], vv[PB];
+        const bool first = tb == t0 + warp;
 #pragma unroll
         for (int j = 0; j < PB; j++) {
             const int t = tb + j * kWarps;
-            if (t < t1) {
+            if (t < t1 && (!first || t == T - 1)) {  // the newest row, and every batch after the first
                 kv[j] = *reinterpret_cast<const RV*>(kbase + (int64_t)t * HD);
                 vv[j] = *reinterpret_cast<const RV*>(vbase + (int64_t)t * HD);
             }
@@ -358,6 +389,29 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
 #pragma unroll
         for (int w = 0; w < kWarps; w++) o += w_o[w][c] * expf(w_m[w] - M);
     }
+    if constexpr (CL) {
+        __shared__ float r_o[8][HD];
+        __shared__ float r_m[8], r_l[8];
+        if (work) {
+            if (c < HD) cluster_store(cluster_map(&r_o[split][c], 0), o);
+            if (c == 0) {
+                cluster_store(cluster_map(&r_m[split], 0), M);
+                cluster_store(cluster_map(&r_l[split], 0), L);
+            }
+        }
+        cluster_sync();
+        if (split != 0) return;
+        float GM = r_m[0];
+        for (int s = 1; s < active; s++) GM = fmaxf(GM, r_m[s]);
+        float GL = 0.f, go = 0.f;
+        for (int s = 0; s < active; s++) {
+            const float w = expf(r_m[s] - GM);
+            GL += r_l[s] * w;
+            if (c < HD) go += r_o[s][c] * w;
+        }
+        if (c < HD) out[c] = cast_out<CT>(go / GL);
+        return;
+    }
     if (active == 1) {
         if (c < HD) out[c] = cast_out<CT>(o / L);
         return;
@@ -370,11 +424,15 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     if (threadIdx.x == 0) ticket_sh = atomicAdd(a.counters + head, 1u);
     __syncthreads();
     if (ticket_sh != (unsigned)(active - 1)) return;
-    // last CTA of this head: merge the splits. Each split's weight exp(m_s - M) / L is computed
-    // once (by thread s) so that the per-column sums are plain independent loads.
+    // last CTA of this head: merge the splits. The record columns are requested together with the
+    // per-split maxima and sums (one round trip through L2), eight splits at a time.
     __threadfence();
     __shared__ float sp_m[64], sp_w[64];
     const float* recs = a.scratch + (int64_t)head * a.n_split * (HD + 2);
+    constexpr int MB = 8;
+    float rv[MB];
+#pragma unroll
+    for (int s = 0; s < MB; s++) rv[s] = (c < HD && s < active) ? __ldcg(recs + s * (HD + 2) + c) : 0.f;
     if (threadIdx.x < active) {
         sp_m[threadIdx.x] = __ldcg(recs + threadIdx.x * (HD + 2) + HD);
         sp_w[threadIdx.x] = __ldcg(recs + threadIdx.x * (HD + 2) + HD + 1);
@@ -389,8 +447,11 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     __syncthreads();
     if (c < HD) {
         float go = 0.f;
+#pragma unroll
+        for (int s = 0; s < MB; s++)
+            if (s < active) go += rv[s] * sp_w[s];
 #pragma unroll 4
-        for (int s = 0; s < active; s++) go += __ldcg(recs + s * (HD + 2) + c) * sp_w[s];
+        for (int s = MB; s < active; s++) go += __ldcg(recs + s * (HD + 2) + c) * sp_w[s];
         out[c] = cast_out<CT>(go);
     }
     if (threadIdx.x == 0) a.counters[head] = 0;  // ready for the next launch
@@ -417,21 +478,38 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
     lc.blockDim = dim3(kThreads);
     lc.dynamicSmemBytes = smem;
     lc.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = allow_pdl ? 1 : 0;
     static const bool use_fast = getenv("RLB_ATTN_FAST") == nullptr || atoi(getenv("RLB_ATTN_FAST")) != 0;
+    static const bool use_cluster = getenv("RLB_ATTN_CLUSTER") == nullptr || atoi(getenv("RLB_ATTN_CLUSTER")) != 0;
     if (use_fast && (a.hd == 64 || a.hd == 128)) {
         lc.dynamicSmemBytes = 0;
-        if (cache_dtype == RLB_F16) {
-            if (a.hd == 128) RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<__half, 128>, a));
-            else RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<__half, 64>, a));
-        } else {
-            if (a.hd == 128) RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<float, 128>, a));
-            else RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_fast_kernel<float, 64>, a));
+        // the splits of a head as one thread-block cluster (portable cluster sizes end at 8)
+        const bool cluster = use_cluster && a.n_split <= 8;
+        if (cluster) {
+            cudaLaunchAttribute& ca = attr[lc.numAttrs++];
+            ca.id = cudaLaunchAttributeClusterDimension;
+            ca.val.clusterDim.x = 1;
+            ca.val.clusterDim.y = (unsigned)a.n_split;
+            ca.val.clusterDim.z = 1;
         }
+        const void* kern;
+        if (cache_dtype == RLB_F16) {
+            if (a.hd == 128) kern = cluster ? (const void*)attn_decode_fast_kernel<__half, 128, true> : (const void*)attn_decode_fast_kernel<__half, 128, false>;
+            else kern = cluster ? (const void*)attn_decode_fast_kernel<__half, 64, true> : (const void*)attn_decode_fast_kernel<__half, 64, false>;
+        } else {
+            if (a.hd == 128) kern = cluster ? (const void*)attn_decode_fast_kernel<float, 128, true> : (const void*)attn_decode_fast_kernel<float, 128, false>;
+            else kern = cluster ? (const void*)attn_decode_fast_kernel<float, 64, true> : (const void*)attn_decode_fast_kernel<float, 64, false>;
+        }
+        // same shared-memory split as the projection kernels before and after this one, so that their
+        // CTAs (which prefetch weights while they wait for this kernel) can share an SM with these
+        static const bool carve = getenv("RLB_CARVE") == nullptr || atoi(getenv("RLB_CARVE")) != 0;
+        if (carve) RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        void* kargs[] = {(void*)&a};
+        RLB_CUDA(cudaLaunchKernelExC(&lc, kern, kargs));
     } else if (cache_dtype == RLB_F16) {
         static bool set = false;
         if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }

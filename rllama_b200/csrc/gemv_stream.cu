@@ -11,9 +11,14 @@
 // on the previous kernel, so the ring is already full when the activation row arrives.
 //
 // Work split: a CTA owns whole row tiles (RB rows x all of K); inside a tile the eight
-// consumer warps split K. Their per-lane partial sums go through shared memory to a tenth
-// warp that folds them in a fixed order and runs the fused epilogue, so the consumers never
-// stop at a CTA-wide barrier and results do not depend on the grid size.
+// consumer warps split K. Each warp folds its lanes' partial sums with a halving exchange
+// (9 shuffles for 8 rows) and hands one value per row to a tenth warp, which adds the eight
+// warps in a fixed order and runs the fused epilogue, so the consumers never stop at a
+// CTA-wide barrier and results do not depend on the grid size.
+//
+// Prologue latency is what separates consecutive kernels, so its loads are written as explicit
+// batches (volatile asm): the RMSNorm gains before the dependency wait, then the residual row
+// and the partial sums in one round trip through L2, all kept in registers.
 //
 // Every wait on an mbarrier is bounded: when a wait runs out the kernel raises an error flag
 // in global memory, switches to a mode in which no wait blocks, and runs to its end.
@@ -67,6 +72,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+// Loads as volatile asm: the compiler keeps them where they are written (all requests of a batch
+// first, uses later; nothing sinks below the dependency wait), so a batch costs one round trip.
+__device__ __forceinline__ float4 ld_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -133,12 +150,36 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Sums N per-lane values over the warp with N - 1 + log2(32 / N) shuffles instead of 5 N: each
+// halving step hands half of the values to the partner lane. Afterwards every lane holds the
+// warp total of value number lane / (32 / N).
+template <int N, int O = 16>
+__device__ __forceinline__ float warp_fold(float (&v)[N], int lane) {
+    if constexpr (N == 1) {
+        float r = v[0];
+#pragma unroll
+        for (int o = O; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+        return r;
+    } else {
+        const bool up = (lane & O) != 0;
+        float h[N / 2];
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) {
+            const float keep = up ? v[i + N / 2] : v[i];
+            const float send = up ? v[i] : v[i + N / 2];
+            h[i] = keep + __shfl_xor_sync(0xffffffffu, send, O);
+        }
+        return warp_fold<N / 2, O / 2>(h, lane);
+    }
+}
+
 struct StreamCfg {
     int n_stages;
     int* err;
 };
-
-template <typename WT, int RB, int J, int PRO, int EPI>
+// G: float4 groups of the activation row a consumer thread holds in the norm prologue (4: rows of up
+// to 4096 elements, 8: up to 8192).
+template <typename WT, int RB, int J, int PRO, int EPI, int G>
 __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs a, const StreamCfg cfg) {
     constexpr int VEC = Vec<WT>::N;
     constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
@@ -154,10 +195,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
     unsigned char* p = smem_raw + (size_t)S * STAGE_BYTES;
     WT* act = reinterpret_cast<WT*>(p);
     p += (((size_t)K * sizeof(WT)) + 15) & ~(size_t)15;
-    float* tmp = reinterpret_cast<float*>(p);
-    if (PRO == PRO_NORM) p += (size_t)K * sizeof(float);
-    float* partial = reinterpret_cast<float*>(p);  // [kPartialDepth][NSEG][kConsumers]
-    p += sizeof(float) * kPartialDepth * NSEG * kConsumers;
+    float* partial = reinterpret_cast<float*>(p);  // [kPartialDepth][NSEG][kConsumerWarps]
+    p += sizeof(float) * kPartialDepth * NSEG * kConsumerWarps;
     float* red = reinterpret_cast<float*>(p);
     p += sizeof(float) * kConsumerWarps;
     p = reinterpret_cast<unsigned char*>(((uintptr_t)p + 7) & ~(uintptr_t)7);
@@ -211,14 +250,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         return;
     }
 
-    // RMSNorm gains never change: fetch this thread's share before waiting for the previous kernel
-    constexpr int kGainRegs = 32;
-    float gain_r[kGainRegs];
-    if (PRO == PRO_NORM && warp < kConsumerWarps) {
+    // RMSNorm gains never change: fetch this thread's share before waiting for the previous kernel.
+    // A consumer thread owns the four elements at tid * 4 + g * 4 * kConsumers of the row, g < kRowGroups.
+    constexpr int kRowGroups = G;
+    constexpr bool kGainEarly = G <= 4;  // with 8 groups the registers are needed for the row itself
+    float4 gain_r[kRowGroups];
+    if (PRO == PRO_NORM && kGainEarly && warp < kConsumerWarps) {
 #pragma unroll
-        for (int q = 0; q < kGainRegs; q++) {
-            const int i = tid + q * kConsumers;
-            gain_r[q] = i < K ? a.gain[i] : 0.f;
+        for (int g = 0; g < kRowGroups; g++) {
+            const int i = tid * 4 + g * 4 * kConsumers;
+            gain_r[g] = i < K ? ld_f4(a.gain + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
 
@@ -231,29 +272,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int row0 = tile * RB;
             mbar_wait(&pfull[ps], pph, dead, cfg.err);
-            const float* pp = partial + (size_t)ps * NSEG * kConsumers;
-            float tot[NSEG];
+            const float* pp = partial + (size_t)ps * NSEG * kConsumerWarps;
+            float mine = 0.f;  // lane i < NSEG: the dot product of row segment i
+            if (lane < NSEG) {
 #pragma unroll
-            for (int i = 0; i < NSEG; i++) {
-                float t = 0.f;
-#pragma unroll
-                for (int w = 0; w < kConsumerWarps; w++) t += pp[i * kConsumers + w * 32 + lane];  // fixed order
-                tot[i] = warp_sum(t);
+                for (int w = 0; w < kConsumerWarps; w++) mine += pp[lane * kConsumerWarps + w];  // fixed order
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&pempty[ps]);
             if (++ps == kPartialDepth) { ps = 0; pph ^= 1u; }
-            auto total = [&](int i) {
-                float t = tot[0];
-#pragma unroll
-                for (int q = 1; q < NSEG; q++) t = (i == q) ? tot[q] : t;
-                return t;
-            };
+            auto total = [&](int i) { return __shfl_sync(0xffffffffu, mine, i & 31); };
             if (EPI == EPI_STORE) {
-                if (lane < RB) reinterpret_cast<WT*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = cast_to<WT>(total(lane));
+                if (lane < RB) reinterpret_cast<WT*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = cast_to<WT>(mine);
             } else if (EPI == EPI_F32) {
                 if (lane < RB) {
-                    const float v = total(lane);
+                    const float v = mine;
                     if (a.n_outs == 0) {
                         reinterpret_cast<float*>(a.out)[(int64_t)(row0 + lane) * a.out_stride] = v;
                     } else {
@@ -263,20 +296,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                     }
                 }
             } else if (EPI == EPI_SWIGLU) {
+                const float up3 = total(RB + lane);
                 if (lane < RB) {
-                    const float a1 = maybe_round<WT>(total(lane));
-                    const float a3 = maybe_round<WT>(total(RB + lane));
+                    const float a1 = maybe_round<WT>(mine);
+                    const float a3 = maybe_round<WT>(up3);
                     const float sg = a1 / (1.0f + expf(-a1));
                     reinterpret_cast<WT*>(a.out)[row0 + lane] = cast_to<WT>(__fmul_rn(sg, a3));
                 }
             } else if (EPI == EPI_QKV) {
+                const float t_re = total(2 * lane), t_im = total(2 * lane + 1);
                 if (lane < RB / 2) {
                     const int pos = *a.pos_ptr;
                     const int row = row0 + 2 * lane;
                     const int sec = row / a.nq, rr = row - sec * a.nq;
                     const int head = rr / a.hd, c = rr - head * a.hd;
-                    const float re = maybe_round<WT>(total(2 * lane));
-                    const float im = maybe_round<WT>(total(2 * lane + 1));
+                    const float re = maybe_round<WT>(t_re);
+                    const float im = maybe_round<WT>(t_im);
                     const float* f = a.rope + ((int64_t)pos * (a.hd / 2) + (c >> 1)) * 2;
                     const float fr = f[0], fi = f[1];
                     const float o_re = __fsub_rn(__fmul_rn(re, fr), __fmul_rn(im, fi));  // src/transformer.rs:844-847
@@ -300,11 +335,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
     if (PRO == PRO_COPY) {
         const uint4* src = reinterpret_cast<const uint4*>(a.vec_in);
         uint4* dst = reinterpret_cast<uint4*>(act);
-        for (int i = tid; i < K / VEC; i += kConsumers) dst[i] = src[i];
+        const int nv = K / VEC;
+        for (int i0 = tid; i0 < nv; i0 += 8 * kConsumers) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (i0 + u * kConsumers < nv) v[u] = ld_u4(src + i0 + u * kConsumers);
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (i0 + u * kConsumers < nv) dst[i0 + u * kConsumers] = v[u];
+        }
     } else {
         const float* xin = a.x_in;
         if (a.tok_ptr) xin += (int64_t)(*a.tok_ptr) * K;
         float ss = 0.f;
+        float4 xr[kRowGroups];  // this thread's elements of the residual row
         if (a.ll_inbox != nullptr) {
             // Tensor-parallel push exchange. This CTA owns a slice of the residual row: it collects
             // that slice's partial sums from every rank's entries (rank order, f16 rounding after the
@@ -342,28 +387,60 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                 if (!ok) { *dead = 1; atomicExch(cfg.err, 2); }
             }
             consumer_sync();
-            for (int i = tid * 4; i < K; i += kConsumers * 4) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(a.x_out + i));
-                *reinterpret_cast<float4*>(tmp + i) = v;
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+#pragma unroll
+            for (int g = 0; g < kRowGroups; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a.x_out + i));
+                    xr[g] = v;
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                }
             }
         } else {
-            for (int i = tid * 4; i < K; i += kConsumers * 4) {
-                float4 v = *reinterpret_cast<const float4*>(xin + i);
-                if (a.n_parts > 0) {
-                    float4 sacc = *reinterpret_cast<const float4*>(a.parts + i);
-                    for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
-                        const float4 t = *reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i);
-                        sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
-                    }
-                    if (a.round_parts) {
-                        sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
-                    }
-                    v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+            // all loads first (the conditional store below may alias them as far as the compiler knows,
+            // which would otherwise serialise the groups: one L2 round trip each)
+            float4 pr[kRowGroups];
+#pragma unroll
+            for (int g = 0; g < kRowGroups; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) {
+                    xr[g] = ld_f4(xin + i);
+                    if (a.n_parts > 0) pr[g] = ld_f4(a.parts + i);
                 }
-                *reinterpret_cast<float4*>(tmp + i) = v;
-                if (blockIdx.x == 0 && a.x_out) *reinterpret_cast<float4*>(a.x_out + i) = v;
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+#pragma unroll
+            for (int g = 0; g < kRowGroups; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) {
+                    float4 v = xr[g];
+                    if (a.n_parts > 0) {
+                        float4 sacc = pr[g];
+                        for (int q = 1; q < a.n_parts; q++) {  // fixed rank order
+                            const float4 t = *reinterpret_cast<const float4*>(a.parts + q * a.part_stride + i);
+                            sacc.x += t.x; sacc.y += t.y; sacc.z += t.z; sacc.w += t.w;
+                        }
+                        if (a.round_parts) {
+                            sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
+                        }
+                        v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+                    }
+                    xr[g] = v;
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                }
+            }
+            if (blockIdx.x == 0 && a.x_out) {
+#pragma unroll
+                for (int g = 0; g < kRowGroups; g++) {
+                    const int i = tid * 4 + g * 4 * kConsumers;
+                    if (i < K) *reinterpret_cast<float4*>(a.x_out + i) = xr[g];
+                }
+            }
+        }
+        if (!kGainEarly) {
+#pragma unroll
+            for (int g = 0; g < kRowGroups; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) gain_r[g] = ld_f4(a.gain + i);
             }
         }
         ss = warp_sum(ss);
@@ -374,12 +451,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         for (int w = 0; w < kConsumerWarps; w++) tot += red[w];
         const float scale = 1.0f / sqrtf(tot / (float)K + a.eps);
 #pragma unroll
-        for (int q = 0; q < kGainRegs; q++) {
-            const int i = tid + q * kConsumers;
-            if (i < K) act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), gain_r[q]));
+        for (int g = 0; g < kRowGroups; g++) {
+            const int i = tid * 4 + g * 4 * kConsumers;
+            if (i < K) {
+                act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(xr[g].x, scale), gain_r[g].x));
+                act[i + 1] = cast_to<WT>(__fmul_rn(__fmul_rn(xr[g].y, scale), gain_r[g].y));
+                act[i + 2] = cast_to<WT>(__fmul_rn(__fmul_rn(xr[g].z, scale), gain_r[g].z));
+                act[i + 3] = cast_to<WT>(__fmul_rn(__fmul_rn(xr[g].w, scale), gain_r[g].w));
+            }
         }
-        for (int i = tid + kGainRegs * kConsumers; i < K; i += kConsumers)
-            act[i] = cast_to<WT>(__fmul_rn(__fmul_rn(tmp[i], scale), a.gain[i]));
     }
     consumer_sync();
 
@@ -411,11 +491,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
             if (lane == 0) mbar_arrive(&empty[s]);
             if (++s == S) { s = 0; ph ^= 1u; }
         }
-        // hand the per-lane partial sums of this tile to the epilogue warp
+        // fold across the warp and hand one partial sum per row segment to the epilogue warp
+        const float folded = warp_fold<NSEG>(acc, lane);
         mbar_wait(&pempty[ps], pph ^ 1u, dead, cfg.err);
-        float* mine = partial + (size_t)ps * NSEG * kConsumers + tid;
-#pragma unroll
-        for (int i = 0; i < NSEG; i++) mine[i * kConsumers] = acc[i];
+        if ((lane & (32 / NSEG - 1)) == 0) partial[((size_t)ps * NSEG + lane / (32 / NSEG)) * kConsumerWarps + warp] = folded;
         __syncwarp();
         if (lane == 0) mbar_arrive(&pfull[ps]);
         if (++ps == kPartialDepth) { ps = 0; pph ^= 1u; }
@@ -427,7 +506,6 @@ struct StreamTuning {
     int stage_kb = 32;   // 16, 32 or 64
     int max_stages = kMaxStages;
     int pdl = 1;
-    int j2 = 0;          // prefer two vectors per lane and half the rows
     int rb = 0;          // explicit rows per tile (0 = from stage_kb)
     int smem_kb = 192;   // shared memory per CTA; the rest of the SM stays free for small co-resident CTAs
 } g_st;
@@ -438,20 +516,18 @@ void load_tuning() {
     if (const char* s = getenv("RLB_STREAM_STAGE_KB")) { int v = atoi(s); g_st.stage_kb = v >= 64 ? 64 : v >= 32 ? 32 : 16; }
     if (const char* s = getenv("RLB_STREAM_STAGES")) { int v = atoi(s); if (v >= 2 && v <= kMaxStages) g_st.max_stages = v; }
     if (const char* s = getenv("RLB_STREAM_PDL")) g_st.pdl = atoi(s) != 0;
-    if (const char* s = getenv("RLB_STREAM_J2")) g_st.j2 = atoi(s) != 0;
     if (const char* s = getenv("RLB_STREAM_RB")) g_st.rb = atoi(s);
     if (const char* s = getenv("RLB_STREAM_SMEM_KB")) { int v = atoi(s); if (v >= 48 && v <= 224) g_st.smem_kb = v; }
 }
 
-template <typename WT, int RB, int J, int PRO, int EPI>
+template <typename WT, int RB, int J, int PRO, int EPI, int G>
 int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     constexpr int VEC = Vec<WT>::N;
     constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
     constexpr size_t STAGE_BYTES = (size_t)NMAT * RB * J * 8 * 32 * VEC * sizeof(WT);
-    auto kern = gemv_stream_kernel<WT, RB, J, PRO, EPI>;
+    auto kern = gemv_stream_kernel<WT, RB, J, PRO, EPI, G>;
     size_t fixed = (((size_t)a.K * sizeof(WT)) + 15) & ~(size_t)15;
-    if (PRO == PRO_NORM) fixed += (size_t)a.K * sizeof(float);
-    fixed += sizeof(float) * kPartialDepth * NMAT * RB * kConsumers + sizeof(float) * kConsumerWarps + 16 +
+    fixed += sizeof(float) * kPartialDepth * NMAT * RB * kConsumerWarps + sizeof(float) * kConsumerWarps + 16 +
              (2 * kMaxStages + 2 * kPartialDepth) * sizeof(uint64_t);
     const size_t budget = (size_t)g_st.smem_kb * 1024;
     if (fixed + 2 * STAGE_BYTES > budget) return rlb_fail(RLB_ERR_LIMIT, "gemv: activation row of %d elements leaves no room for the weight ring", a.K);
@@ -461,10 +537,15 @@ int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     static bool attr_set = false;
     if (!attr_set) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        // every kernel of the decode chain asks for the same shared-memory split, so that CTAs of
+        // consecutive kernels can share an SM
+        if (getenv("RLB_CARVE") == nullptr || atoi(getenv("RLB_CARVE")) != 0)
+            RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
     const int n_tiles = a.rows / RB;
-    int grid = n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
+    const int max_grid = ctx->sm_count;
+    int grid = n_tiles < max_grid ? n_tiles : max_grid;
     StreamCfg cfg;
     cfg.n_stages = stages;
     cfg.err = err_flag;
@@ -489,7 +570,7 @@ ShapeCfg pick_cfg(int epilogue, const GemvArgs& a) {
     load_tuning();
     const int nmat = (epilogue == EPI_SWIGLU) ? 2 : 1;
     const int unit = (epilogue == EPI_QKV) ? a.nq : a.rows;
-    const int J = g_st.j2 ? 2 : 1;  // stage = nmat * RB * J * 4 KB
+    const int J = 1;  // stage = nmat * RB * 4 KB
     int RB = g_st.rb > 0 ? g_st.rb / nmat : g_st.stage_kb / 4 / nmat / J;
     if (RB > 8) RB = 8;
     if (RB < 1) RB = 1;
@@ -504,20 +585,19 @@ int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     constexpr int NMAT = (EPI == EPI_SWIGLU) ? 2 : 1;
     const ShapeCfg sc = pick_cfg(EPI, a);
     if (sc.rb == 0) return RLB_ERR_STATE;  // caller falls back to the register-staged kernel
-    if (sc.j == 1) {
-        switch (sc.rb) {
-            case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI>(ctx, a, err_flag, pdl);
-            case 4: return launch_cfg<WT, 4, 1, PRO, EPI>(ctx, a, err_flag, pdl);
-            case 2: return launch_cfg<WT, 2, 1, PRO, EPI>(ctx, a, err_flag, pdl);
-            default: break;
-        }
-    } else {
-        switch (sc.rb) {
-            case 8: return launch_cfg<WT, (NMAT == 1 ? 8 : 4), 2, PRO, EPI>(ctx, a, err_flag, pdl);
-            case 4: return launch_cfg<WT, 4, 2, PRO, EPI>(ctx, a, err_flag, pdl);
-            case 2: return launch_cfg<WT, 2, 2, PRO, EPI>(ctx, a, err_flag, pdl);
-            default: break;
-        }
+    // (the two-vectors-per-lane variants J = 2 were measured slower at every shape and are not built)
+    const bool wide = PRO == PRO_NORM && a.K > 4096;
+    switch (sc.rb) {
+        case 8:
+            return wide ? launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+                        : launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
+        case 4:
+            return wide ? launch_cfg<WT, 4, 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+                        : launch_cfg<WT, 4, 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
+        case 2:
+            return wide ? launch_cfg<WT, 2, 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+                        : launch_cfg<WT, 2, 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
+        default: break;
     }
     return RLB_ERR_STATE;
 }
@@ -535,7 +615,8 @@ int launch_typed(rlb_ctx* ctx, int prologue, int epilogue, const GemvArgs& a, in
 
 static bool stream_shape_ok(rlb_dtype dtype, int prologue, const GemvArgs& a) {
     const int vec = dtype == RLB_F16 ? 8 : 4;
-    if (a.K <= 0 || a.rows < 2 || a.K % vec != 0 || a.ldw % vec != 0 || (prologue == PRO_NORM && a.K % 4 != 0)) return false;
+    if (a.K <= 0 || a.rows < 2 || a.K % vec != 0 || a.ldw % vec != 0) return false;
+    if (prologue == PRO_NORM && (a.K % 4 != 0 || a.K > 8192)) return false;  // the norm keeps the row in registers
     if ((a.ldw * (int64_t)(dtype == RLB_F16 ? 2 : 4)) % 16 != 0) return false;  // bulk copies need 16-byte aligned rows
     return true;
 }
@@ -545,7 +626,8 @@ int gemv_stream_grid(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, 
     const ShapeCfg sc = pick_cfg(epilogue, a);
     if (sc.rb == 0) return 0;
     const int n_tiles = a.rows / sc.rb;
-    return n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count;
+    const int max_grid = ctx->sm_count;
+    return n_tiles < max_grid ? n_tiles : max_grid;
 }
 
 // Returns RLB_ERR_STATE (without recording an error message) when the shape is not handled

@@ -506,6 +506,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
     const bool f16 = m->wdt == RLB_F16;
     const int round_proj = (f16 && m->tp == 1) ? 1 : 0;  // with tensor parallelism the rounding follows the reduction
     RLB_TRY(launch_embed(ctx, m->tok_emb, m->pf_tokens, n, d, m->pf_x));
+
     for (int l = 0; l < m->p.n_layers; l++) {
         const LayerW& W = m->L[l];
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
@@ -642,6 +643,8 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
     const int max_ns = (p->max_seq_len + 63) / 64;
     if (ns > max_ns) ns = max_ns;
     if (ns > 32) ns = 32;
+    // up to 8 splits run as one thread-block cluster per head and merge through distributed shared memory
+    if (ns > 8 && (getenv("RLB_ATTN_CLUSTER") == nullptr || atoi(getenv("RLB_ATTN_CLUSTER")) != 0)) ns = 8;
     if (ns < 1) ns = 1;
     if (const char* e = getenv("RLB_ATTN_SPLIT")) { int v = atoi(e); if (v >= 1 && v <= 64) ns = v; }
     m->n_split = ns;
