@@ -84,6 +84,21 @@ def test_7b_shape_two_layers(cuda_ctx, f16):
         assert max(rel_err(a, b) for a, b in zip(gl, ol)) <= F32_REL
 
 
+@pytest.mark.parametrize("dim,heads", [(5120, 40), (8192, 64)])
+def test_wide_rows_one_layer(cuda_ctx, dim, heads):
+    """Rows of more than 4096 elements (the 13B and 65B widths): the norm prologue holds the row in
+    eight register groups; the attended context grows past two attention splits."""
+    cfg = cfg_variant("tiny", dim=dim, n_heads=heads, ffn=1536, n_layers=1, vocab=1024, max_seq_len=160)
+    gpu, orc = build_pair(cfg, True, cuda_ctx)
+    prompt = S.synth_tokens(126, cfg["vocab"])
+    ot, ol = greedy_protocol(orc, prompt, 6)
+    caches = gpu.make_caches()
+    gl = [gpu.forward(prompt, 0, caches)]
+    for i, tok in enumerate(ot):
+        gl.append(gpu.forward([tok], len(prompt) + i, caches))
+    assert max(float(np.abs(a - b).max()) for a, b in zip(gl, ol)) <= F16_ABS
+
+
 def test_odd_head_dim_and_ffn_shapes(cuda_ctx):
     """head_dim 64 and 128, FFN widths that are not multiples of the tile sizes."""
     for over in (dict(dim=256, n_heads=2, ffn=696, n_layers=2, vocab=1000), dict(dim=384, n_heads=6, ffn=1032, n_layers=1, vocab=512)):
