@@ -244,6 +244,48 @@ int rlb_model_params_from_json(const char* path, rlb_model_params* out);
  * keeps its slice.                                                                       */
 int rlb_model_from_llama_source(rlb_ctx* ctx, rlb_data_source* ds, const rlb_model_params* params, rlb_model** out);
 
+/* ------------------------------------------------------------------------------------
+ * Host-side callers of the path: tokenizer and sampler of the generation loop
+ * (src/rllama_main.rs:814-901).
+ * ---------------------------------------------------------------------------------- */
+typedef struct rlb_tokenizer rlb_tokenizer;  /* `Tokenizer` (src/tokenizer.rs:11-14) */
+typedef struct rlb_sampler rlb_sampler;      /* `TokenSampler` (src/token_sampler.rs:6-11) */
+
+/* Tokenizer::load (src/tokenizer.rs:46-96): a SentencePiece ModelProto file.          */
+int rlb_tokenizer_load(const char* path, rlb_tokenizer** out);
+int rlb_tokenizer_free(rlb_tokenizer* tk);
+/* Number of pieces in the model file (indices run 0 .. n-1; pieces without text and
+ * earlier duplicates of a text have no entry).                                          */
+int rlb_tokenizer_n_pieces(rlb_tokenizer* tk, int32_t* n);
+/* Tokenizer::id_to_str (src/tokenizer.rs:100-108). The reference panics on an unknown
+ * id; this returns RLB_ERR_INVALID. *out stays valid until rlb_tokenizer_free.          */
+int rlb_tokenizer_id_to_str(rlb_tokenizer* tk, int32_t id, const char** out);
+/* Tokenizer::str_to_id (src/tokenizer.rs:111-118): *id = -1 when there is no such piece. */
+int rlb_tokenizer_str_to_id(rlb_tokenizer* tk, const char* s, int32_t* id);
+/* Tokenizer::tokenize_to_ids (src/tokenizer.rs:166-178): start token 1, then the greedy
+ * longest-prefix pieces of "\u2581" + text with spaces replaced by "\u2581". *n receives
+ * the count; ids may be NULL to query it, else RLB_ERR_LIMIT when cap is too small.      */
+int rlb_tokenizer_tokenize_to_ids(rlb_tokenizer* tk, const char* text, int32_t* ids, int32_t cap, int32_t* n);
+
+/* TokenSampler::new (src/token_sampler.rs:20-28): temperature 0.2, top_p 1.0, top_k 1,
+ * repetition_penalty 0.8.                                                               */
+int rlb_sampler_create(rlb_sampler** out);
+int rlb_sampler_free(rlb_sampler* s);
+/* The four builder setters / getters (src/token_sampler.rs:30-66) in one call each.     */
+int rlb_sampler_set(rlb_sampler* s, float temperature, float top_p, int32_t top_k, float repetition_penalty);
+int rlb_sampler_get(rlb_sampler* s, float* temperature, float* top_p, int32_t* top_k, float* repetition_penalty);
+/* No counterpart in the reference (it draws from rand::thread_rng): seeds the draw.     */
+int rlb_sampler_seed(rlb_sampler* s, uint64_t seed);
+/* TokenSampler::sample (src/token_sampler.rs:83-174) on `vocab` f32 logits: *token and
+ * its probability among the candidates kept by top-k / top-p.                           */
+int rlb_sampler_sample(rlb_sampler* s, const float* logits, int32_t vocab, const int32_t* existing_tokens, int32_t n_existing,
+                       int32_t* token, float* prob);
+/* The candidate list `sample` draws from (descending probability, after top-k and
+ * top-p): up to cap entries are written, *n receives the list's length. No counterpart
+ * in the reference; it makes the sampler testable without statistics.                   */
+int rlb_sampler_candidates(rlb_sampler* s, const float* logits, int32_t vocab, const int32_t* existing_tokens, int32_t n_existing,
+                           int32_t* tokens, float* probs, int32_t cap, int32_t* n);
+
 /* Tuning and inspection. Options: "graph" (replay the decode step as a CUDA graph, default 1),
  * "stream_gemv" (bulk-copy staged GEMV kernels, default 1), "pdl" (programmatic dependent launch,
  * default 1), "persistent" (one cooperative kernel per token, default 0), "profile" (time every

@@ -26,6 +26,10 @@ EXPORTS = [
     "rlb_model_set_option", "rlb_model_get_stat",
     "rlb_data_source_open", "rlb_data_source_free", "rlb_data_source_shards", "rlb_data_source_tensor_shape",
     "rlb_data_source_read_f16", "rlb_model_params_from_json", "rlb_model_from_llama_source",
+    "rlb_tokenizer_load", "rlb_tokenizer_free", "rlb_tokenizer_n_pieces", "rlb_tokenizer_id_to_str", "rlb_tokenizer_str_to_id",
+    "rlb_tokenizer_tokenize_to_ids",
+    "rlb_sampler_create", "rlb_sampler_free", "rlb_sampler_set", "rlb_sampler_get", "rlb_sampler_seed", "rlb_sampler_sample",
+    "rlb_sampler_candidates",
 ]
 
 
@@ -90,6 +94,15 @@ def lib():
         "rlb_data_source_read_f16": [vp, ctypes.c_char_p, i32, vp, i64, i64],
         "rlb_model_params_from_json": [ctypes.c_char_p, P(ModelParams)],
         "rlb_model_from_llama_source": [vp, vp, P(ModelParams), P(vp)],
+        "rlb_tokenizer_load": [ctypes.c_char_p, P(vp)], "rlb_tokenizer_free": [vp], "rlb_tokenizer_n_pieces": [vp, P(i32)],
+        "rlb_tokenizer_id_to_str": [vp, i32, P(ctypes.c_char_p)], "rlb_tokenizer_str_to_id": [vp, ctypes.c_char_p, P(i32)],
+        "rlb_tokenizer_tokenize_to_ids": [vp, ctypes.c_char_p, vp, i32, P(i32)],
+        "rlb_sampler_create": [P(vp)], "rlb_sampler_free": [vp],
+        "rlb_sampler_set": [vp, ctypes.c_float, ctypes.c_float, i32, ctypes.c_float],
+        "rlb_sampler_get": [vp, P(ctypes.c_float), P(ctypes.c_float), P(i32), P(ctypes.c_float)],
+        "rlb_sampler_seed": [vp, ctypes.c_uint64],
+        "rlb_sampler_sample": [vp, vp, i32, vp, i32, P(i32), P(ctypes.c_float)],
+        "rlb_sampler_candidates": [vp, vp, i32, vp, i32, vp, vp, i32, P(i32)],
     }
     for name, args in sig.items():
         fn = getattr(L, name)

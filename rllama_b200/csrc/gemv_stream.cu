@@ -80,6 +80,11 @@ __device__ __forceinline__ float4 ld_f4(const float* p) {
     asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {  // L2 only: data published by other CTAs of this kernel
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint4 ld_u4(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -360,6 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
             const int per = ((K + (int)gridDim.x - 1) / (int)gridDim.x + 3) & ~3;
             const int s0 = min(K, (int)blockIdx.x * per), s1 = min(K, s0 + per);
             for (int i = s0 + tid; i < s1; i += kConsumers) {
+                const float xv = xin[i];  // requested before the poll, so its latency hides behind it
                 float part[RLB_MAX_TP];
                 ll_gather<RLB_MAX_TP>(a.ll_inbox + i, (size_t)K, a.n_parts, seq, part, dead, cfg.err);
                 float sum = part[0];
@@ -367,7 +373,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
                 for (int q = 1; q < RLB_MAX_TP; q++)
                     if (q < a.n_parts) sum += part[q];  // fixed rank order: identical on every rank
                 if (a.round_parts) sum = round_f16(sum);
-                a.x_out[i] = xin[i] + sum;
+                a.x_out[i] = xv + sum;
             }
             // Publish the slice with plain stores, a device-scope fence and one count per CTA; the
             // other CTAs poll that single counter (thousands of threads polling entries would
@@ -390,9 +396,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
 #pragma unroll
             for (int g = 0; g < kRowGroups; g++) {
                 const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) xr[g] = ld_cg_f4(a.x_out + i);  // all requests first: one round trip through L2
+            }
+#pragma unroll
+            for (int g = 0; g < kRowGroups; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
                 if (i < K) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(a.x_out + i));
-                    xr[g] = v;
+                    const float4 v = xr[g];
                     ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
                 }
             }
