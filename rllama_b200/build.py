@@ -11,6 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "librllama_b200.so")
+CLI = os.path.join(HERE, "bin", "rllama-b200")
 SOURCES = ["context.cu", "gemv.cu", "gemv_stream.cu", "decode_mega.cu", "attention.cu", "elementwise.cu", "gemm.cu", "gemm_tc.cu", "model.cu", "tp.cu", "loader.cu", "host.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
@@ -53,7 +54,21 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed: %s\n%s" % (r.stdout, r.stderr))
+    build_cli(force)
     return LIB
+
+
+def build_cli(force=False):
+    """The command-line program (host C++ over the C ABI): ``rllama_b200/bin/rllama-b200``."""
+    src = os.path.join(HERE, "cli", "rllama_cli.cpp")
+    os.makedirs(os.path.dirname(CLI), exist_ok=True)
+    if force or _stale(CLI, [src, LIB, os.path.join(HERE, "..", "include", "rllama_b200.h")]):
+        cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", src, "-o", CLI, "-L" + HERE, "-lrllama_b200",
+               "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + os.path.join(os.path.dirname(NVCC), "..", "lib64")]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("building the command-line program failed: %s\n%s" % (r.stdout, r.stderr))
+    return CLI
 
 
 if __name__ == "__main__":

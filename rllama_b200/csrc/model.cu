@@ -1031,6 +1031,8 @@ int rlb_model_get_stat(rlb_model* m, const char* name, double* value) {
     if (!strcmp(name, "first_head")) { *value = m->head0; return RLB_OK; }
     if (!strcmp(name, "local_ffn")) { *value = m->F; return RLB_OK; }
     if (!strcmp(name, "local_vocab")) { *value = m->V; return RLB_OK; }
+    if (!strcmp(name, "vocab_size")) { *value = m->p.vocab_size; return RLB_OK; }
+    if (!strcmp(name, "ffn_dim")) { *value = m->p.ffn_dim; return RLB_OK; }
     if (!strncmp(name, "prof_ms_", 8)) {
         for (int i = 0; i < PC_COUNT; i++)
             if (!strcmp(name + 8, kProfNames[i])) { *value = m->prof_ms[i]; return RLB_OK; }
