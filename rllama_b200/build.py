@@ -62,7 +62,8 @@ def build_cli(force=False):
     """The command-line program (host C++ over the C ABI): ``rllama_b200/bin/rllama-b200``."""
     src = os.path.join(HERE, "cli", "rllama_cli.cpp")
     os.makedirs(os.path.dirname(CLI), exist_ok=True)
-    if force or _stale(CLI, [src, LIB, os.path.join(HERE, "..", "include", "rllama_b200.h")]):
+    deps = [src, os.path.join(HERE, "cli", "inference_server.hpp"), LIB, os.path.join(HERE, "..", "include", "rllama_b200.h")]
+    if force or _stale(CLI, deps):
         cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-Wall", src, "-o", CLI, "-L" + HERE, "-lrllama_b200",
                "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + os.path.join(os.path.dirname(NVCC), "..", "lib64")]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -8,7 +8,7 @@
 //    `--percentage-to-gpu` is accepted and ignored (every layer is resident in HBM);
 //  * `--f16` alone selects f16 weights and caches (the reference's OpenCL build forces f16);
 //  * `--seed` (no counterpart) seeds the sampler's draw, which the reference takes from thread_rng;
-//  * `--inference-server` is refused as in a reference build without its `server` feature.
+//  * `--inference-server` runs the HTTP server of inference_server.hpp (the reference: rocket).
 #include <unistd.h>
 
 #include <charconv>
@@ -26,6 +26,7 @@
 #include <vector>
 
 #include "../../include/rllama_b200.h"
+#include "inference_server.hpp"
 
 namespace {
 
@@ -44,6 +45,9 @@ struct Cli {
     std::optional<long> cuda_device;
     std::optional<float> percentage_to_gpu;
     bool inference_server = false;
+    std::optional<long> inference_server_port, inference_server_max_concurrent_inferences, inference_server_prompt_cache_size;
+    std::optional<std::string> inference_server_host, inference_server_api_path;
+    bool inference_server_exit_after_one_query = false;
     std::optional<uint64_t> seed;
 };
 
@@ -64,7 +68,9 @@ void print_help() {
         "      --interactive-prompt-postfix <TEXT>\n      --interactive-prompt-prefix <TEXT>\n      --start-interactive\n"
         "      --max-seq-len <N>\n      --temperature <T>\n      --top-p <P>\n      --top-k <K>\n      --repetition-penalty <R>\n"
         "      --max-threads <N>\n      --f16\n      --cuda-device <N> (alias --opencl-device)\n      --percentage-to-gpu <P> (ignored)\n"
-        "      --seed <N>\n      --inference-server (not built)\n  -h, --help");
+        "      --seed <N>\n      --inference-server\n      --inference-server-port <PORT>\n      --inference-server-host <HOST>\n"
+        "      --inference-server-max-concurrent-inferences <N>\n      --inference-server-api-path <PATH>\n"
+        "      --inference-server-prompt-cache-size <N>\n      --inference-server-exit-after-one-query\n  -h, --help");
 }
 
 template <typename T>
@@ -120,9 +126,15 @@ Cli parse_cli(int argc, char** argv) {
         else if (name == "percentage-to-gpu") c.percentage_to_gpu = parse_number<float>(name, value());
         else if (name == "seed") c.seed = parse_number<uint64_t>(name, value());
         else if (name == "inference-server") flag(&c.inference_server);
-        else if (name == "inference-server-exit-after-one-query") { bool ignored; flag(&ignored); }
-        else if (name == "inference-server-port" || name == "inference-server-host" || name == "inference-server-max-concurrent-inferences" ||
-                 name == "inference-server-api-path" || name == "inference-server-prompt-cache-size") (void)value();
+        else if (name == "inference-server-exit-after-one-query") flag(&c.inference_server_exit_after_one_query);
+        else if (name == "inference-server-port") {
+            c.inference_server_port = parse_number<long>(name, value());
+            if (*c.inference_server_port < 0 || *c.inference_server_port > 65535) usage_error("invalid value for '--inference-server-port': not a 16-bit port");
+        }
+        else if (name == "inference-server-host") c.inference_server_host = value();
+        else if (name == "inference-server-max-concurrent-inferences") c.inference_server_max_concurrent_inferences = parse_number<long>(name, value());
+        else if (name == "inference-server-api-path") c.inference_server_api_path = value();
+        else if (name == "inference-server-prompt-cache-size") c.inference_server_prompt_cache_size = parse_number<long>(name, value());
         else usage_error("unexpected argument '--" + name + "' found");
     }
     if (!have_model || !have_tok || !have_param) {
@@ -363,10 +375,6 @@ static void run(const Cli& cli) {
     }
     const std::string interactive_prompt_prefix = cli.interactive_prompt_prefix.value_or(" ");
     const std::string interactive_prompt_postfix = cli.interactive_prompt_postfix.value_or("### Assistant:");
-    if (cli.inference_server) {
-        std::fprintf(stderr, "Inference server is not enabled in this build.\n");
-        throw Failure{"Inference server is not enabled in this build."};
-    }
     const long max_threads = cli.max_threads.value_or((long)std::thread::hardware_concurrency());
 
     bool be_quiet = !should_colorize();
@@ -388,8 +396,8 @@ static void run(const Cli& cli) {
     } else if (!cli.prompt && cli.prompt_file) {
         pln("Using prompt file: " + *cli.prompt_file);
         prompt = read_file(*cli.prompt_file);
-    } else if (!(cli.start_interactive && !cli.prompt && !cli.prompt_file)) {
-        // neither or both given; only interactive mode may start without a prompt
+    } else if (!(cli.start_interactive || cli.inference_server) || cli.prompt || cli.prompt_file) {
+        // neither or both given; only interactive mode and the server may start without a prompt
         std::fprintf(stderr, "Please provide either a prompt or a prompt file.\n");
         throw Failure{"Please provide either a prompt or a prompt file."};
     }
@@ -420,6 +428,27 @@ static void run(const Cli& cli) {
     // from the embedding table, and that is the length of the logits
     double vocab = 0;
     ok(rlb_model_get_stat(model, "vocab_size", &vocab));
+    if (cli.inference_server) {
+        // server_inference (src/rllama_main.rs:317-386)
+        const long port = cli.inference_server_port.value_or(8080);
+        const std::string host = cli.inference_server_host.value_or("127.0.0.1");
+        const long concurrent = cli.inference_server_max_concurrent_inferences.value_or(5);
+        const std::string api_path = cli.inference_server_api_path.value_or("/rllama/v1/inference");
+        const long cache_size = cli.inference_server_prompt_cache_size.value_or(50);
+        pln("Maximum concurrent inferences: " + std::to_string(concurrent));
+        pln("Prompt cache size: " + std::to_string(cache_size));
+        pln("Maximum sequence length: " + std::to_string(max_seq_len));
+        pln("--- Starting HTTP server on " + host + ":" + std::to_string(port) + ", answering to requests at " + api_path + " ---");
+        std::fflush(stdout);
+        server::ServerState state((size_t)std::max(0L, cache_size), (size_t)std::max(1L, concurrent));
+        state.model = model;
+        state.tokenizer = tk;
+        state.vocab = (int32_t)vocab;
+        state.max_seq_len = (size_t)max_seq_len;
+        state.exit_after_one_query = cli.inference_server_exit_after_one_query;
+        const std::string why = server::serve(&state, host, (int)port, api_path);
+        throw Failure{"Starting web server failed. (" + why + ")"};
+    }
     command_line_inference(cli, model, tk, prompt, interactive_stop, interactive_system_prompt, interactive_prompt_prefix,
                            interactive_prompt_postfix, cli.start_interactive, be_quiet, max_seq_len, params, (int32_t)vocab, max_threads);
     rlb_model_free(model);

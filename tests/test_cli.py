@@ -34,9 +34,11 @@ def test_cli_flag_errors_need_no_device():
     assert r.returncode == 2 and "invalid value 'many' for '--top-k'" in r.stderr
     r = run_cli(base + ["--temperature"])
     assert r.returncode == 2 and "a value is required" in r.stderr
-    # a build of the reference without its server feature refuses the flag the same way
+    r = run_cli(base + ["--inference-server-port", "99999"])
+    assert r.returncode == 2 and "--inference-server-port" in r.stderr
+    # nothing to load at these paths (and no device on a CPU box): an error, not a crash
     r = run_cli(base + ["--inference-server", "--inference-server-port", "8080"])
-    assert r.returncode == 1 and "Inference server is not enabled in this build." in r.stderr
+    assert r.returncode == 1 and r.stderr.startswith("Error: ")
     assert run_cli(["--help"]).returncode == 0
 
 
@@ -109,3 +111,130 @@ def test_cli_generates_the_same_text_as_the_python_chain(tmp_path, cuda_ctx):
     assert r.returncode == 0 and r.stdout == prompt + text + "\n"
     r = run_cli(["--model-path", str(tmp_path / "nowhere")] + args[2:])
     assert r.returncode == 1 and r.stderr.startswith("Error: ")
+
+
+def _free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _post(port, path, body, method="POST"):
+    import http.client
+    c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+    c.request(method, path, body=body, headers={"Content-Type": "application/json"})
+    r = c.getresponse()
+    data = r.read().decode("utf-8")
+    c.close()
+    return r.status, data
+
+
+def _start_server(args, port):
+    import time
+    import socket
+    env = dict(os.environ)
+    proc = subprocess.Popen([CLI] + args + ["--inference-server", "--inference-server-port", str(port)], env=env,
+                            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    deadline = time.time() + 120
+    while time.time() < deadline:
+        if proc.poll() is not None:
+            raise AssertionError("server exited: " + proc.stderr.read())
+        try:
+            with socket.create_connection(("127.0.0.1", port), timeout=1):
+                return proc
+        except OSError:
+            time.sleep(0.2)
+    proc.kill()
+    raise AssertionError("server did not start listening")
+
+
+@pytest.mark.gpu
+def test_inference_server_streams_json_lines(tmp_path, cuda_ctx):
+    """POST <api path>: chunked JSON lines, the reference's defaults, checks and status codes
+    (src/rllama_main.rs:388-712), greedy tokens equal to the Python chain's."""
+    import json
+    torch = pytest.importorskip("torch")
+    from checkpoint import write_llama_checkpoint
+    from helpers import cfg_variant
+    from rllama_b200 import DataSettings, DataSource, ModelParams, Tokenizer, Transformer
+    from test_tokenizer_sampler import train_model
+
+    model_bytes, _ = train_model(byte_fallback=True, vocab=400)
+    tok_path = tmp_path / "tokenizer.model"
+    tok_path.write_bytes(model_bytes)
+    cfg = cfg_variant("tiny", dim=256, n_heads=4, n_layers=2, ffn=352, vocab=400, max_seq_len=40)
+    ckpt = tmp_path / "ckpt"
+    os.makedirs(ckpt)
+    write_llama_checkpoint(str(ckpt), cfg)
+    prompt = "kalo miren tas"
+    max_seq = 32
+    tk = Tokenizer.load(tok_path)
+    p = ModelParams.from_json(os.path.join(str(ckpt), "params.json"))
+    model = Transformer.from_unpickled(p.dim, p.n_layers, p.n_heads, max_seq, p.norm_eps, DataSettings(cl=cuda_ctx).force_f16(),
+                                       DataSource.from_llama_source(ckpt))
+    toks = tk.tokenize_to_ids(prompt)
+    n_prompt = len(toks)
+    caches = model.make_caches()
+    want, prev, first_logits = [], 0, None
+    for _ in range(6):
+        logits = model.forward(toks[prev:], prev, caches)
+        if first_logits is None:
+            first_logits = logits.copy()
+        prev = len(toks)
+        toks.append(int(np.argmax(logits)))
+        want.append(tk.id_to_str(toks[-1]))
+
+    args = ["--model-path", str(ckpt), "--tokenizer-path", str(tok_path), "--param-path", os.path.join(str(ckpt), "params.json"),
+            "--max-seq-len", str(max_seq), "--f16", "--inference-server-prompt-cache-size", "4"]
+    port = _free_port()
+    proc = _start_server(args, port)
+    try:
+        path = "/rllama/v1/inference"
+        status, body = _post(port, path, json.dumps({"prompt": prompt, "top_k": 1, "max_new_tokens": 6}))
+        assert status == 200
+        lines = [json.loads(l) for l in body.splitlines()]
+        assert [list(l.keys())[0] for l in lines] == want
+        assert all(list(l.values())[0] == {"p": 1.0} or list(l.values())[0] == {"p": 1.0, "is_end_token": True} for l in lines)
+        # the same request again (served from the cache repository, which holds 4 sequences at most) and with a trailing slash
+        status, body2 = _post(port, path + "/", json.dumps({"prompt": prompt, "top_k": 1, "max_new_tokens": 6, "ignored": [1, {"a": None}]}))
+        assert status == 200 and body2 == body
+        # defaults: 20 new tokens, bounded by the sequence length
+        status, body3 = _post(port, path, json.dumps({"prompt": prompt}))
+        assert status == 200 and 1 <= len(body3.splitlines()) <= 20
+        status, body4 = _post(port, path, json.dumps({"prompt": prompt, "top_k": 1, "max_seq_len": n_prompt + 2, "max_new_tokens": 10}))
+        assert status == 200 and body4.splitlines() == body.splitlines()[:2]
+        status, body5 = _post(port, path, json.dumps({"prompt": prompt, "top_k": 1, "max_seq_len": 10 ** 6, "max_new_tokens": 1000}))
+        assert status == 200 and len(body5.splitlines()) == max_seq - n_prompt
+        # every piece with its logit
+        status, body6 = _post(port, path, json.dumps({"prompt": prompt, "no_token_sampling": True, "max_new_tokens": 1}))
+        assert status == 200
+        allp = json.loads(body6.splitlines()[0])
+        assert len(allp) == 400 and list(allp.keys()) == sorted(allp.keys(), key=lambda s: s.encode("utf-8"))
+        for i in (0, 1, 2, 13, 57, 399):
+            assert abs(allp[tk.id_to_str(i)]["p"] - float(first_logits[i])) <= 1e-6 * max(1.0, abs(float(first_logits[i])))
+        assert allp["</s>"].get("is_end_token") is True and "is_end_token" not in allp["<s>"]
+        # the reference's refusals
+        for bad, text in (("{not json", "Invalid JSON."), (json.dumps({"top_k": 3}), "Invalid JSON."), (json.dumps({"prompt": 5}), "Invalid JSON."),
+                          (json.dumps({"prompt": "x", "top_k": -1}), "Invalid JSON."), (json.dumps({"prompt": "x", "top_k": 1.5}), "Invalid JSON."),
+                          (json.dumps({"prompt": "x", "top_k": 0}), "Top-k must be greater than 0."),
+                          ('{"prompt": "x", "prompt": "y"}', "Invalid JSON.")):
+            status, msg = _post(port, path, bad)
+            assert (status, msg) == (400, text), bad
+        assert _post(port, "/elsewhere", "{}")[0] == 404
+        assert _post(port, path, None, method="GET")[0] == 404
+        assert proc.poll() is None
+    finally:
+        proc.kill()
+        proc.wait()
+    # --inference-server-exit-after-one-query: one answer, then the process ends with status 0
+    port = _free_port()
+    proc = _start_server(args + ["--inference-server-exit-after-one-query", "--inference-server-api-path", "/v1"], port)
+    try:
+        status, body7 = _post(port, "/v1", json.dumps({"prompt": prompt, "top_k": 1, "max_new_tokens": 6}))
+        assert status == 200 and body7 == body
+        assert proc.wait(timeout=60) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+            proc.wait()
