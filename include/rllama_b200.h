@@ -233,6 +233,17 @@ int rlb_data_source_tensor_shape(rlb_data_source* ds, const char* name, int32_t 
 /* TensorBuilder::load_from_pieces (src/tensor.rs:2388-2545): reads the f16 rows of every
  * shard from consolidated.NN/data/<key> into out[rows][cols] (dense, f16 bit patterns).  */
 int rlb_data_source_read_f16(rlb_data_source* ds, const char* name, int32_t direction, uint16_t* out, int64_t rows, int64_t cols);
+/* DataSource::from_vicuna_source (src/data_source.rs:206-215): a HuggingFace directory
+ * (config.json, pytorch_model.bin.index.json, *.bin torch.save archives read in place).   */
+int rlb_data_source_open_vicuna(const char* model_path, rlb_data_source** out);
+/* DataSource::from_inferred_source (src/data_source.rs:188-204): params.json -> Meta's
+ * layout, pytorch_model.bin.index.json -> HuggingFace's, else "Unknown source".           */
+int rlb_data_source_open_inferred(const char* model_path, rlb_data_source** out);
+/* DataSource::need_to_do_antitranspose (src/data_source.rs:223-228).                      */
+int rlb_data_source_need_antitranspose(rlb_data_source* ds, int32_t* yes);
+/* Tensor::huggingface_llama_model_antitranspose (src/tensor.rs:841-909) on dense f16 rows:
+ * dst row h*hd + 2j + t = src row h*hd + t*hd/2 + j, hd = rows / n_heads.                 */
+int rlb_huggingface_antitranspose_f16(const uint16_t* src, uint16_t* dst, int64_t rows, int64_t cols, int32_t n_heads);
 /* ModelParams from params.json (src/model_params.rs:4-14, src/rllama_main.rs:201-241):
  * fills dim, n_heads, n_layers, norm_eps, vocab_size (HF aliases accepted); the other
  * fields of *out are left untouched.                                                     */

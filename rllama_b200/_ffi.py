@@ -26,6 +26,8 @@ EXPORTS = [
     "rlb_model_set_option", "rlb_model_get_stat",
     "rlb_data_source_open", "rlb_data_source_free", "rlb_data_source_shards", "rlb_data_source_tensor_shape",
     "rlb_data_source_read_f16", "rlb_model_params_from_json", "rlb_model_from_llama_source",
+    "rlb_data_source_open_vicuna", "rlb_data_source_open_inferred", "rlb_data_source_need_antitranspose",
+    "rlb_huggingface_antitranspose_f16",
     "rlb_tokenizer_load", "rlb_tokenizer_free", "rlb_tokenizer_n_pieces", "rlb_tokenizer_id_to_str", "rlb_tokenizer_str_to_id",
     "rlb_tokenizer_tokenize_to_ids",
     "rlb_sampler_create", "rlb_sampler_free", "rlb_sampler_set", "rlb_sampler_get", "rlb_sampler_seed", "rlb_sampler_sample",
@@ -94,6 +96,9 @@ def lib():
         "rlb_data_source_read_f16": [vp, ctypes.c_char_p, i32, vp, i64, i64],
         "rlb_model_params_from_json": [ctypes.c_char_p, P(ModelParams)],
         "rlb_model_from_llama_source": [vp, vp, P(ModelParams), P(vp)],
+        "rlb_data_source_open_vicuna": [ctypes.c_char_p, P(vp)], "rlb_data_source_open_inferred": [ctypes.c_char_p, P(vp)],
+        "rlb_data_source_need_antitranspose": [vp, P(i32)],
+        "rlb_huggingface_antitranspose_f16": [vp, vp, i64, i64, i32],
         "rlb_tokenizer_load": [ctypes.c_char_p, P(vp)], "rlb_tokenizer_free": [vp], "rlb_tokenizer_n_pieces": [vp, P(i32)],
         "rlb_tokenizer_id_to_str": [vp, i32, P(ctypes.c_char_p)], "rlb_tokenizer_str_to_id": [vp, ctypes.c_char_p, P(i32)],
         "rlb_tokenizer_tokenize_to_ids": [vp, ctypes.c_char_p, vp, i32, P(i32)],

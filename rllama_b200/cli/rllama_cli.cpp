@@ -407,7 +407,7 @@ static void run(const Cli& cli) {
     ok(rlb_tokenizer_load(cli.tokenizer_path.c_str(), &tk));
     pln("Tokenizer loaded. Loading model from " + cli.model_path + "...");
     rlb_data_source* ds = nullptr;
-    ok(rlb_data_source_open(cli.model_path.c_str(), &ds));
+    ok(rlb_data_source_open_inferred(cli.model_path.c_str(), &ds));  // DataSource::from_inferred_source (:239)
     rlb_model_params params;
     std::memset(&params, 0, sizeof params);
     ok(rlb_model_params_from_json(cli.param_path.c_str(), &params));

@@ -10,14 +10,24 @@
 // Shards are concatenated along the axis the reference uses for each tensor: rows for wq wk wv
 // w1 w3 output, columns for wo w2 tok_embeddings; gains are taken from the first shard.
 // As in the reference only torch.HalfStorage tensors with contiguous rows are accepted.
+//
+// Second layout (DataSource::VicunaSource, src/huggingface_loader.rs): a HuggingFace directory with
+// config.json, pytorch_model.bin.index.json and *.bin files, each a torch.save zip archive read in
+// place (stored or deflated entries, zip64 records); tensor names are HuggingFace's and the q/k
+// projections carry its rotary row permutation, which is undone on load.
 // Deviation: BININT2 is decoded as unsigned (the reference reads it as i16, src/unpickler.rs:484,
 // which misreads 32768..65535); NEWTRUE, NONE, TUPLE3, SETITEM and an OrderedDict at top level
 // are accepted in addition to the reference's opcode subset.
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <dirent.h>
+#include <zlib.h>
+
+#include <algorithm>
 #include <map>
 #include <memory>
+#include <set>
 #include <sstream>
 
 #include "internal.h"
@@ -162,9 +172,19 @@ bool to_builder(const PVal* v, Builder* out) {
 
 }  // namespace
 
+// One torch.save archive of a HuggingFace / Vicuna checkpoint (src/huggingface_loader.rs:20-27).
+struct ZipEntry { uint64_t data_offset = 0, comp_size = 0, size = 0; int method = 0; };
+struct ZipFile {
+    std::string file;
+    std::map<std::string, ZipEntry> entries;  // by name without its first directory
+    std::set<std::string> tensors;            // tensor names of its data.pkl
+};
+
 struct rlb_data_source {
     std::string path;
-    std::vector<PV> shards;  // one unpickled dict per consolidated.NN
+    std::vector<PV> shards;  // one unpickled dict per consolidated.NN (Vicuna: the merged dict of all archives)
+    bool vicuna = false;     // DataSource::VicunaSource (src/data_source.rs:22-30)
+    std::vector<ZipFile> zips;
 };
 
 namespace {
@@ -199,6 +219,129 @@ int collect(const rlb_data_source* ds, const char* name, int direction, std::vec
     }
     return RLB_OK;
 }
+
+// ---- zip archives (torch.save output; the reference uses the `zip` crate) --------------------
+uint32_t rd32(const unsigned char* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+uint16_t rd16(const unsigned char* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+uint64_t rd64(const unsigned char* p) { return (uint64_t)rd32(p) | ((uint64_t)rd32(p + 4) << 32); }
+
+bool read_at(FILE* f, uint64_t off, void* dst, size_t n) {
+    return fseeko(f, (off_t)off, SEEK_SET) == 0 && fread(dst, 1, n, f) == n;
+}
+
+// huggingface_loader::remove_first_directory (src/huggingface_loader.rs:124-132)
+std::string remove_first_directory(const std::string& name) {
+    const size_t slash = name.find('/');
+    return slash == std::string::npos ? std::string() : name.substr(slash + 1);
+}
+
+// Central directory of a zip file (zip64 records included): every entry with the offset of its data.
+int zip_list(const std::string& path, std::vector<std::pair<std::string, ZipEntry>>* out) {
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) return rlb_fail(RLB_ERR_STATE, "cannot open %s", path.c_str());
+    struct Closer { FILE* f; ~Closer() { fclose(f); } } closer{f};
+    fseeko(f, 0, SEEK_END);
+    const uint64_t fsize = (uint64_t)ftello(f);
+    const uint64_t tail = std::min<uint64_t>(fsize, 65536 + 22 + 20);
+    std::vector<unsigned char> buf((size_t)tail);
+    if (!read_at(f, fsize - tail, buf.data(), (size_t)tail)) return rlb_fail(RLB_ERR_INVALID, "%s: not a zip archive", path.c_str());
+    int64_t eocd = -1;
+    for (int64_t i = (int64_t)tail - 22; i >= 0; i--)
+        if (rd32(&buf[(size_t)i]) == 0x06054b50u) { eocd = i; break; }
+    if (eocd < 0) return rlb_fail(RLB_ERR_INVALID, "%s: not a zip archive (no end-of-central-directory record)", path.c_str());
+    uint64_t n_entries = rd16(&buf[(size_t)eocd + 10]), cd_size = rd32(&buf[(size_t)eocd + 12]), cd_off = rd32(&buf[(size_t)eocd + 16]);
+    if (eocd >= 20 && rd32(&buf[(size_t)eocd - 20]) == 0x07064b50u) {  // zip64 locator -> zip64 end record
+        const uint64_t z64 = rd64(&buf[(size_t)eocd - 20 + 8]);
+        unsigned char rec[56];
+        if (!read_at(f, z64, rec, sizeof rec) || rd32(rec) != 0x06064b50u) return rlb_fail(RLB_ERR_INVALID, "%s: bad zip64 end record", path.c_str());
+        n_entries = rd64(rec + 32); cd_size = rd64(rec + 40); cd_off = rd64(rec + 48);
+    }
+    if (cd_off + cd_size > fsize) return rlb_fail(RLB_ERR_INVALID, "%s: central directory outside the file", path.c_str());
+    std::vector<unsigned char> cd((size_t)cd_size);
+    if (!read_at(f, cd_off, cd.data(), (size_t)cd_size)) return rlb_fail(RLB_ERR_INVALID, "%s: cannot read the central directory", path.c_str());
+    size_t p = 0;
+    for (uint64_t e = 0; e < n_entries; e++) {
+        if (p + 46 > cd.size() || rd32(&cd[p]) != 0x02014b50u) return rlb_fail(RLB_ERR_INVALID, "%s: bad central directory entry", path.c_str());
+        ZipEntry ze;
+        ze.method = rd16(&cd[p + 10]);
+        ze.comp_size = rd32(&cd[p + 20]);
+        ze.size = rd32(&cd[p + 24]);
+        const size_t nlen = rd16(&cd[p + 28]), xlen = rd16(&cd[p + 30]), clen = rd16(&cd[p + 32]);
+        uint64_t local = rd32(&cd[p + 42]);
+        if (p + 46 + nlen + xlen + clen > cd.size()) return rlb_fail(RLB_ERR_INVALID, "%s: truncated central directory", path.c_str());
+        const std::string name((const char*)&cd[p + 46], nlen);
+        // zip64 extended information: the fields that overflowed, in this order
+        for (size_t x = p + 46 + nlen; x + 4 <= p + 46 + nlen + xlen;) {
+            const uint16_t id = rd16(&cd[x]), len = rd16(&cd[x + 2]);
+            if (id == 0x0001) {
+                size_t q = x + 4;
+                if (ze.size == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { ze.size = rd64(&cd[q]); q += 8; }
+                if (ze.comp_size == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { ze.comp_size = rd64(&cd[q]); q += 8; }
+                if (local == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { local = rd64(&cd[q]); q += 8; }
+            }
+            x += 4 + (size_t)len;
+        }
+        unsigned char lh[30];
+        if (!read_at(f, local, lh, sizeof lh) || rd32(lh) != 0x04034b50u) return rlb_fail(RLB_ERR_INVALID, "%s: bad local header of %s", path.c_str(), name.c_str());
+        ze.data_offset = local + 30 + rd16(lh + 26) + rd16(lh + 28);
+        if (ze.method != 0 && ze.method != 8) return rlb_fail(RLB_ERR_INVALID, "%s: %s uses compression method %d (stored and deflate are read)", path.c_str(), name.c_str(), ze.method);
+        out->emplace_back(name, ze);
+        p += 46 + nlen + xlen + clen;
+    }
+    return RLB_OK;
+}
+
+// The bytes [skip, skip + want) of an entry's uncompressed data.
+int zip_read(const std::string& path, const ZipEntry& ze, uint64_t skip, void* dst, uint64_t want) {
+    if (skip + want > ze.size) return rlb_fail(RLB_ERR_STATE, "%s: entry of %llu bytes is too short for %llu bytes at offset %llu", path.c_str(),
+                                               (unsigned long long)ze.size, (unsigned long long)want, (unsigned long long)skip);
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) return rlb_fail(RLB_ERR_STATE, "cannot open %s", path.c_str());
+    struct Closer { FILE* f; ~Closer() { fclose(f); } } closer{f};
+    if (ze.method == 0) {
+        if (!read_at(f, ze.data_offset + skip, dst, (size_t)want)) return rlb_fail(RLB_ERR_STATE, "%s: read error", path.c_str());
+        return RLB_OK;
+    }
+    // deflate: no random access, so the stream is inflated from its start and the prefix dropped
+    // (the reference "seeks" the same way, src/data_source.rs:56-74)
+    if (fseeko(f, (off_t)ze.data_offset, SEEK_SET) != 0) return rlb_fail(RLB_ERR_STATE, "%s: seek failed", path.c_str());
+    z_stream zs;
+    memset(&zs, 0, sizeof zs);
+    if (inflateInit2(&zs, -MAX_WBITS) != Z_OK) return rlb_fail(RLB_ERR_STATE, "zlib: inflateInit2 failed");
+    std::vector<unsigned char> in(1 << 16), scratch(1 << 16);
+    uint64_t remaining_in = ze.comp_size, produced = 0;
+    unsigned char* outp = (unsigned char*)dst;
+    int zr = Z_OK;
+    while (produced < skip + want && zr != Z_STREAM_END) {
+        if (zs.avail_in == 0) {
+            const size_t n = (size_t)std::min<uint64_t>(in.size(), remaining_in);
+            if (n == 0 || fread(in.data(), 1, n, f) != n) { inflateEnd(&zs); return rlb_fail(RLB_ERR_STATE, "%s: truncated deflate stream", path.c_str()); }
+            remaining_in -= n;
+            zs.next_in = in.data();
+            zs.avail_in = (uInt)n;
+        }
+        zs.next_out = scratch.data();
+        zs.avail_out = (uInt)scratch.size();
+        zr = inflate(&zs, Z_NO_FLUSH);
+        if (zr != Z_OK && zr != Z_STREAM_END) { inflateEnd(&zs); return rlb_fail(RLB_ERR_STATE, "%s: corrupt deflate stream", path.c_str()); }
+        const uint64_t got = scratch.size() - zs.avail_out;
+        // copy the part of [produced, produced + got) that falls into [skip, skip + want)
+        const uint64_t lo = std::max<uint64_t>(produced, skip), hi = std::min<uint64_t>(produced + got, skip + want);
+        if (hi > lo) memcpy(outp + (lo - skip), scratch.data() + (lo - produced), (size_t)(hi - lo));
+        produced += got;
+    }
+    inflateEnd(&zs);
+    if (produced < skip + want) return rlb_fail(RLB_ERR_STATE, "%s: deflate stream ended early", path.c_str());
+    return RLB_OK;
+}
+
+bool file_exists(const std::string& p) {
+    std::ifstream f(p);
+    return (bool)f;
+}
+
+// serde_json::from_str::<HugginfaceConfig> requires these keys (src/huggingface_loader.rs:29-44)
+bool json_has_key(const std::string& text, const char* key) { return text.find(std::string("\"") + key + "\"") != std::string::npos; }
 
 // A number that follows "key": in a flat JSON object (ModelParams is five scalars).
 bool json_number(const std::string& text, const char* key, double* out) {
@@ -238,6 +381,109 @@ int rlb_data_source_open(const char* model_path, rlb_data_source** out) {
     return RLB_OK;
 }
 
+// DataSource::from_vicuna_source (src/data_source.rs:206-215) with HugginfaceModel::unpickle
+// (src/huggingface_loader.rs:58-121): config.json and pytorch_model.bin.index.json must parse, every
+// *.bin file of the directory is a torch.save zip whose data.pkl dicts are merged into one.
+int rlb_data_source_open_vicuna(const char* model_path, rlb_data_source** out) {
+    if (!model_path || !out) return rlb_fail(RLB_ERR_INVALID, "rlb_data_source_open_vicuna: null pointer");
+    *out = nullptr;
+    std::unique_ptr<rlb_data_source> ds(new rlb_data_source());
+    ds->path = model_path;
+    ds->vicuna = true;
+    auto slurp = [](const std::string& p, std::string* text) {
+        std::ifstream f(p);
+        if (!f) return false;
+        std::stringstream ss;
+        ss << f.rdbuf();
+        *text = ss.str();
+        return true;
+    };
+    std::string config, index;
+    if (!slurp(ds->path + "/config.json", &config)) return rlb_fail(RLB_ERR_STATE, "cannot open %s/config.json", model_path);
+    for (const char* key : {"vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "max_position_embeddings",
+                            "rms_norm_eps", "architectures", "bos_token_id", "eos_token_id", "torch_dtype"})
+        if (!json_has_key(config, key)) return rlb_fail(RLB_ERR_INVALID, "Error parsing JSON: %s/config.json: missing field `%s`", model_path, key);
+    if (!slurp(ds->path + "/pytorch_model.bin.index.json", &index)) return rlb_fail(RLB_ERR_STATE, "cannot open %s/pytorch_model.bin.index.json", model_path);
+    for (const char* key : {"metadata", "total_size", "weight_map"})
+        if (!json_has_key(index, key)) return rlb_fail(RLB_ERR_INVALID, "Error parsing JSON: %s/pytorch_model.bin.index.json: missing field `%s`", model_path, key);
+    std::vector<std::string> bins;
+    if (DIR* d = opendir(model_path)) {
+        while (dirent* e = readdir(d)) {
+            const std::string n = e->d_name;
+            if (n.size() > 4 && n.compare(n.size() - 4, 4, ".bin") == 0) bins.push_back(ds->path + "/" + n);
+        }
+        closedir(d);
+    } else {
+        return rlb_fail(RLB_ERR_STATE, "cannot list %s", model_path);
+    }
+    std::sort(bins.begin(), bins.end());
+    PV merged = mk(PVal::DICT);
+    for (const std::string& bin : bins) {
+        std::vector<std::pair<std::string, ZipEntry>> entries;
+        RLB_TRY(zip_list(bin, &entries));
+        ZipFile zf;
+        zf.file = bin;
+        for (auto& kv : entries) {
+            zf.entries[remove_first_directory(kv.first)] = kv.second;
+            const std::string& n = kv.first;
+            if (n.size() >= 8 && n.compare(n.size() - 8, 8, "data.pkl") == 0) {
+                std::vector<unsigned char> bytes((size_t)kv.second.size);
+                RLB_TRY(zip_read(bin, kv.second, 0, bytes.data(), kv.second.size));
+                PV root;
+                std::string why;
+                if (unpickle(bytes, &root, &why) != RLB_OK) return rlb_fail(RLB_ERR_INVALID, "%s:%s: %s", bin.c_str(), n.c_str(), why.c_str());
+                if (root->kind != PVal::DICT) return rlb_fail(RLB_ERR_INVALID, "%s:%s: top level is not a dict", bin.c_str(), n.c_str());
+                for (auto& item : root->dict) {
+                    if (item.first->kind != PVal::STR) continue;
+                    zf.tensors.insert(item.first->s);
+                    // Value::merge_dicts (src/unpickler.rs:91-108): later archives replace earlier entries
+                    bool replaced = false;
+                    for (auto& have : merged->dict)
+                        if (have.first->kind == PVal::STR && have.first->s == item.first->s) { have.second = item.second; replaced = true; break; }
+                    if (!replaced) merged->dict.push_back(item);
+                }
+            }
+        }
+        ds->zips.push_back(std::move(zf));
+    }
+    ds->shards.push_back(merged);
+    *out = ds.release();
+    return RLB_OK;
+}
+
+// DataSource::from_inferred_source (src/data_source.rs:188-204): params.json marks Meta's layout,
+// pytorch_model.bin.index.json the HuggingFace one.
+int rlb_data_source_open_inferred(const char* model_path, rlb_data_source** out) {
+    if (!model_path || !out) return rlb_fail(RLB_ERR_INVALID, "rlb_data_source_open_inferred: null pointer");
+    const std::string p = model_path;
+    if (file_exists(p + "/params.json")) return rlb_data_source_open(model_path, out);
+    if (file_exists(p + "/pytorch_model.bin.index.json")) return rlb_data_source_open_vicuna(model_path, out);
+    *out = nullptr;
+    return rlb_fail(RLB_ERR_INVALID, "Unknown source");
+}
+
+// DataSource::need_to_do_antitranspose (src/data_source.rs:223-228)
+int rlb_data_source_need_antitranspose(rlb_data_source* ds, int32_t* yes) {
+    if (!ds || !yes) return rlb_fail(RLB_ERR_INVALID, "rlb_data_source_need_antitranspose: null pointer");
+    *yes = ds->vicuna ? 1 : 0;
+    return RLB_OK;
+}
+
+// Tensor::huggingface_llama_model_antitranspose (src/tensor.rs:841-909): the rows of a head, stored by
+// HuggingFace as [2][head_dim / 2] (all even rotary components, then all odd ones), go back to the
+// interleaved [head_dim / 2][2] order of Meta's files.
+int rlb_huggingface_antitranspose_f16(const uint16_t* src, uint16_t* dst, int64_t rows, int64_t cols, int32_t n_heads) {
+    if (!src || !dst) return rlb_fail(RLB_ERR_INVALID, "rlb_huggingface_antitranspose_f16: null pointer");
+    if (n_heads <= 0 || rows % n_heads != 0 || (rows / n_heads) % 2 != 0)
+        return rlb_fail(RLB_ERR_INVALID, "antitranspose: %lld rows do not split into %d heads of even size", (long long)rows, n_heads);
+    const int64_t hd = rows / n_heads, half = hd / 2;
+    for (int64_t h = 0; h < n_heads; h++)
+        for (int64_t two = 0; two < 2; two++)
+            for (int64_t j = 0; j < half; j++)
+                memcpy(dst + (h * hd + j * 2 + two) * cols, src + (h * hd + two * half + j) * cols, (size_t)cols * 2);
+    return RLB_OK;
+}
+
 int rlb_data_source_free(rlb_data_source* ds) {
     delete ds;
     return RLB_OK;
@@ -264,6 +510,18 @@ int rlb_data_source_read_f16(rlb_data_source* ds, const char* name, int32_t dire
     RLB_TRY(collect(ds, name, direction, &bs, &r, &c));
     if (r != rows || c != cols) return rlb_fail(RLB_ERR_INVALID, "%s is %lldx%lld, the buffer is %lldx%lld", name, (long long)r, (long long)c, (long long)rows, (long long)cols);
     int64_t row0 = 0, col0 = 0;
+    if (ds->vicuna) {
+        // DataSource::open for a Vicuna source (src/data_source.rs:111-160): the archive that holds both the
+        // storage file and the tensor's name
+        const Builder& b = bs[0];
+        const std::string entry = "data/" + b.file;
+        for (const ZipFile& zf : ds->zips) {
+            auto it = zf.entries.find(entry);
+            if (it == zf.entries.end() || !zf.tensors.count(name)) continue;
+            return zip_read(zf.file, it->second, (uint64_t)b.offset * 2, out, (uint64_t)rows * cols * 2);
+        }
+        return rlb_fail(RLB_ERR_STATE, "file not found: %s", entry.c_str());
+    }
     for (size_t i = 0; i < bs.size(); i++) {
         const Builder& b = bs[i];
         const std::string path = shard_dir(ds, i) + "/data/" + b.file;
@@ -306,40 +564,55 @@ int rlb_model_params_from_json(const char* path, rlb_model_params* out) {
 // Transformer::from_unpickled (src/transformer.rs:242-326) + Embedding::from_unpickled (src/embedding.rs:13-48).
 // params: dim, n_layers, n_heads, norm_eps from params.json; max_seq_len, force_f16, tp_rank, tp_size from the
 // caller; ffn_dim and vocab_size are taken from the tensors (w1 rows, embedding rows), as in the reference.
+// Every tensor is looked up under Meta's name first and under its HuggingFace name second (the reference's
+// from_unpickled_pieces2 / get_str_key2); wq and wk of a HuggingFace source are un-permuted
+// (src/transformer.rs:619-622).
 int rlb_model_from_llama_source(rlb_ctx* ctx, rlb_data_source* ds, const rlb_model_params* params, rlb_model** out) {
     if (!ctx || !ds || !params || !out) return rlb_fail(RLB_ERR_INVALID, "rlb_model_from_llama_source: null pointer");
     *out = nullptr;
     rlb_model_params p = *params;
+    auto pick = [&](const std::string& meta, const std::string& hf) -> std::string {
+        if (!ds->shards.empty() && dict_get(ds->shards[0], meta) == nullptr && dict_get(ds->shards[0], hf) != nullptr) return hf;
+        return meta;  // (a name missing under both spellings is reported under Meta's)
+    };
     int64_t r = 0, c = 0;
-    RLB_TRY(rlb_data_source_tensor_shape(ds, "tok_embeddings.weight", 1, &r, &c));
+    const std::string emb = pick("tok_embeddings.weight", "model.embed_tokens.weight");
+    RLB_TRY(rlb_data_source_tensor_shape(ds, emb.c_str(), 1, &r, &c));
     p.vocab_size = (int32_t)r;
-    if (c != p.dim) return rlb_fail(RLB_ERR_INVALID, "tok_embeddings.weight has %lld columns, params say dim %d", (long long)c, p.dim);
-    RLB_TRY(rlb_data_source_tensor_shape(ds, "layers.0.feed_forward.w1.weight", 0, &r, &c));
+    if (c != p.dim) return rlb_fail(RLB_ERR_INVALID, "%s has %lld columns, params say dim %d", emb.c_str(), (long long)c, p.dim);
+    RLB_TRY(rlb_data_source_tensor_shape(ds, pick("layers.0.feed_forward.w1.weight", "model.layers.0.mlp.gate_proj.weight").c_str(), 0, &r, &c));
     p.ffn_dim = (int32_t)r;
     rlb_model* m = nullptr;
     RLB_TRY(rlb_model_create(ctx, &p, &m));
-    std::vector<uint16_t> buf;
+    std::vector<uint16_t> buf, tmp;
     auto load = [&](const std::string& name, int direction, rlb_tensor_kind kind, int layer) -> int {
         int64_t rows = 0, cols = 0;
         RLB_TRY(rlb_data_source_tensor_shape(ds, name.c_str(), direction, &rows, &cols));
         buf.resize((size_t)rows * cols);
         RLB_TRY(rlb_data_source_read_f16(ds, name.c_str(), direction, buf.data(), rows, cols));
+        if (ds->vicuna && (kind == RLB_WQ || kind == RLB_WK)) {
+            tmp.resize(buf.size());
+            RLB_TRY(rlb_huggingface_antitranspose_f16(buf.data(), tmp.data(), rows, cols, p.n_heads));
+            buf.swap(tmp);
+        }
         return rlb_model_set_tensor(m, kind, layer, buf.data(), rows, cols, cols, RLB_F16);
     };
-    int s = load("tok_embeddings.weight", 1, RLB_TOK_EMBEDDINGS, 0);
+    int s = load(emb, 1, RLB_TOK_EMBEDDINGS, 0);
     for (int l = 0; l < p.n_layers && s == RLB_OK; l++) {
-        const std::string pre = "layers." + std::to_string(l) + ".";
-        struct { const char* suffix; int direction; rlb_tensor_kind kind; } items[] = {
-            {"attention.wq.weight", 0, RLB_WQ}, {"attention.wk.weight", 0, RLB_WK}, {"attention.wv.weight", 0, RLB_WV},
-            {"attention.wo.weight", 1, RLB_WO}, {"feed_forward.w1.weight", 0, RLB_W1}, {"feed_forward.w2.weight", 1, RLB_W2},
-            {"feed_forward.w3.weight", 0, RLB_W3}, {"attention_norm.weight", 2, RLB_ATTENTION_NORM}, {"ffn_norm.weight", 2, RLB_FFN_NORM}};
+        const std::string pre = "layers." + std::to_string(l) + ".", hpre = "model.layers." + std::to_string(l) + ".";
+        struct { const char* suffix; const char* hf; int direction; rlb_tensor_kind kind; } items[] = {
+            {"attention.wq.weight", "self_attn.q_proj.weight", 0, RLB_WQ}, {"attention.wk.weight", "self_attn.k_proj.weight", 0, RLB_WK},
+            {"attention.wv.weight", "self_attn.v_proj.weight", 0, RLB_WV}, {"attention.wo.weight", "self_attn.o_proj.weight", 1, RLB_WO},
+            {"feed_forward.w1.weight", "mlp.gate_proj.weight", 0, RLB_W1}, {"feed_forward.w2.weight", "mlp.down_proj.weight", 1, RLB_W2},
+            {"feed_forward.w3.weight", "mlp.up_proj.weight", 0, RLB_W3}, {"attention_norm.weight", "input_layernorm.weight", 2, RLB_ATTENTION_NORM},
+            {"ffn_norm.weight", "post_attention_layernorm.weight", 2, RLB_FFN_NORM}};
         for (auto& it : items) {
-            s = load(pre + it.suffix, it.direction, it.kind, l);
+            s = load(pick(pre + it.suffix, hpre + it.hf), it.direction, it.kind, l);
             if (s != RLB_OK) break;
         }
     }
-    if (s == RLB_OK) s = load("norm.weight", 2, RLB_NORM, 0);
-    if (s == RLB_OK) s = load("output.weight", 0, RLB_OUTPUT, 0);
+    if (s == RLB_OK) s = load(pick("norm.weight", "model.norm.weight"), 2, RLB_NORM, 0);
+    if (s == RLB_OK) s = load(pick("output.weight", "lm_head.weight"), 0, RLB_OUTPUT, 0);
     if (s == RLB_OK) s = rlb_model_finalize(m);
     if (s != RLB_OK) {
         rlb_model_free(m);

@@ -38,6 +38,26 @@ class DataSource:
         check(_ffi.lib().rlb_data_source_open(str(path).encode(), ctypes.byref(h)))
         return cls(h, path)
 
+    @classmethod
+    def from_vicuna_source(cls, path):
+        """``DataSource::from_vicuna_source``: a HuggingFace directory (``config.json``,
+        ``pytorch_model.bin.index.json``, ``*.bin`` torch.save archives)."""
+        h = ctypes.c_void_p()
+        check(_ffi.lib().rlb_data_source_open_vicuna(str(path).encode(), ctypes.byref(h)))
+        return cls(h, path)
+
+    @classmethod
+    def from_inferred_source(cls, path):
+        """``DataSource::from_inferred_source`` (``src/data_source.rs:188-204``)."""
+        h = ctypes.c_void_p()
+        check(_ffi.lib().rlb_data_source_open_inferred(str(path).encode(), ctypes.byref(h)))
+        return cls(h, path)
+
+    def need_to_do_antitranspose(self):
+        v = ctypes.c_int32()
+        check(_ffi.lib().rlb_data_source_need_antitranspose(self._h, ctypes.byref(v)))
+        return bool(v.value)
+
     def shards(self):
         n = ctypes.c_int32()
         check(_ffi.lib().rlb_data_source_shards(self._h, ctypes.byref(n)))
@@ -65,3 +85,12 @@ class DataSource:
             self.close()
         except Exception:
             pass
+
+
+def huggingface_llama_model_antitranspose(w, n_heads):
+    """``Tensor::huggingface_llama_model_antitranspose`` (``src/tensor.rs:841-909``) on a float16 matrix."""
+    w = np.ascontiguousarray(w, dtype=np.float16)
+    out = np.empty_like(w)
+    check(_ffi.lib().rlb_huggingface_antitranspose_f16(w.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p),
+                                                       w.shape[0], w.shape[1], int(n_heads)))
+    return out

@@ -60,7 +60,7 @@ class Transformer:
     @classmethod
     def from_unpickled(cls, dim, n_layers, n_heads, max_seq_len, eps, data_settings, data_source, tp_rank=0, tp_size=1):
         """``Transformer::from_unpickled(emb, dim, n_layers, n_heads, max_seq_len, eps, data_settings,
-        data_source)``: loads every tensor of a LLaMA checkpoint by its Meta name (the embedding
+        data_source)``: loads every tensor of a LLaMA checkpoint by its Meta or HuggingFace name (the embedding
         table included; FFN width and vocabulary size come from the tensors)."""
         self = cls.__new__(cls)
         ds = data_settings or DataSettings()
@@ -69,8 +69,8 @@ class Transformer:
         self._h = ctypes.c_void_p()
         check(_ffi.lib().rlb_model_from_llama_source(self.cl._h, data_source._h, ctypes.byref(p), ctypes.byref(self._h)))
         self.dim, self.n_layers, self.n_heads = dim, n_layers, n_heads
-        self.ffn_dim = data_source.tensor_shape("layers.0.feed_forward.w1.weight", 0)[0]
-        self.vocab_size = data_source.tensor_shape("tok_embeddings.weight", 1)[0]
+        self.ffn_dim = int(self.get_stat("ffn_dim"))        # from the w1 tensor
+        self.vocab_size = int(self.get_stat("vocab_size"))  # from the embedding table
         self.max_seq_len, self.eps, self.force_f16 = max_seq_len, eps, ds._force_f16
         self.tp_rank, self.tp_size = tp_rank, tp_size
         return self

@@ -79,3 +79,63 @@ def python_unpickle(path):
 
     with open(path, "rb") as f:
         return U(f).load()
+
+
+HF_NAMES = {
+    "tok_embeddings": "model.embed_tokens.weight", "norm": "model.norm.weight", "output": "lm_head.weight",
+    "wq": "model.layers.{l}.self_attn.q_proj.weight", "wk": "model.layers.{l}.self_attn.k_proj.weight",
+    "wv": "model.layers.{l}.self_attn.v_proj.weight", "wo": "model.layers.{l}.self_attn.o_proj.weight",
+    "w1": "model.layers.{l}.mlp.gate_proj.weight", "w2": "model.layers.{l}.mlp.down_proj.weight",
+    "w3": "model.layers.{l}.mlp.up_proj.weight", "attention_norm": "model.layers.{l}.input_layernorm.weight",
+    "ffn_norm": "model.layers.{l}.post_attention_layernorm.weight",
+}
+
+
+def hf_permute(w, n_heads):
+    """What HuggingFace's conversion does to wq / wk: per head, the interleaved rotary pairs
+    [hd/2][2] become [2][hd/2] (all even components first)."""
+    rows, cols = w.shape
+    hd = rows // n_heads
+    return np.ascontiguousarray(w.reshape(n_heads, hd // 2, 2, cols).transpose(0, 2, 1, 3).reshape(rows, cols))
+
+
+def write_hf_checkpoint(path, cfg, seed=1234, n_files=2, deflate=False):
+    """A HuggingFace-style directory (config.json, pytorch_model.bin.index.json, *.bin torch.save
+    archives) holding the same synthetic weights as write_llama_checkpoint, with HuggingFace's tensor
+    names and its q/k row permutation. Returns {hf name: float16 array as stored}."""
+    import torch
+    os.makedirs(path, exist_ok=True)
+    stored = {}
+    for kind, layer in S.tensor_list(cfg):
+        t = S.synth_tensor(kind, layer, cfg, seed).astype(np.float16)
+        if kind in ("wq", "wk"):
+            t = hf_permute(t, cfg["n_heads"])
+        if kind in REPLICATED:
+            t = t.reshape(-1)
+        stored[HF_NAMES[kind].format(l=layer)] = t
+    names = list(stored)
+    weight_map = {}
+    for i in range(n_files):
+        fname = "pytorch_model-%05d-of-%05d.bin" % (i + 1, n_files)
+        part = {n: torch.from_numpy(np.ascontiguousarray(stored[n])).clone() for n in names[i::n_files]}
+        for n in part:
+            weight_map[n] = fname
+        buf = io.BytesIO()
+        torch.save(part, buf)
+        raw = buf.getvalue()
+        if deflate:  # the same members, compressed (the reference reads these through the zip crate)
+            out = io.BytesIO()
+            with zipfile.ZipFile(io.BytesIO(raw)) as zin, zipfile.ZipFile(out, "w", zipfile.ZIP_DEFLATED) as zout:
+                for info in zin.infolist():
+                    zout.writestr(info.filename, zin.read(info))
+            raw = out.getvalue()
+        with open(os.path.join(path, fname), "wb") as f:
+            f.write(raw)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump({"vocab_size": cfg["vocab"], "hidden_size": cfg["dim"], "intermediate_size": cfg["ffn"],
+                   "num_hidden_layers": cfg["n_layers"], "num_attention_heads": cfg["n_heads"],
+                   "max_position_embeddings": cfg["max_seq_len"], "rms_norm_eps": cfg["norm_eps"], "architectures": ["LlamaForCausalLM"],
+                   "bos_token_id": 1, "eos_token_id": 2, "torch_dtype": "float16"}, f)
+    with open(os.path.join(path, "pytorch_model.bin.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": int(sum(v.nbytes for v in stored.values()))}, "weight_map": weight_map}, f)
+    return stored

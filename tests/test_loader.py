@@ -9,7 +9,7 @@ import pytest
 from rllama_b200 import DataSource, ModelParams, RllamaError
 from rllama_b200 import synthetic as S
 from rllama_b200.data_source import COLS, FIRST, ROWS
-from checkpoint import NAMES, python_unpickle, write_llama_checkpoint
+from checkpoint import HF_NAMES, NAMES, hf_permute, python_unpickle, write_hf_checkpoint, write_llama_checkpoint
 from helpers import cfg_variant
 
 torch = pytest.importorskip("torch")
@@ -77,6 +77,65 @@ def test_loader_errors(tmp_path):
     open(tmp_path / "junk" / "consolidated.00" / "data.pkl", "wb").write(b"hello")
     with pytest.raises(RllamaError):
         DataSource.from_llama_source(tmp_path / "junk")
+
+
+@pytest.mark.parametrize("deflate", [False, True])
+def test_huggingface_source_reads_archives_in_place(tmp_path, deflate):
+    """DataSource::from_vicuna_source / from_inferred_source and the q/k anti-transpose."""
+    from rllama_b200.data_source import huggingface_llama_model_antitranspose
+    cfg = small()
+    stored = write_hf_checkpoint(str(tmp_path / "hf"), cfg, n_files=2, deflate=deflate)
+    ds = DataSource.from_inferred_source(tmp_path / "hf")
+    assert ds.need_to_do_antitranspose() and ds.shards() == 1
+    for name, want in stored.items():
+        got = ds.tensor(name, FIRST if want.ndim == 1 else ROWS)
+        assert np.array_equal(got.view(np.uint16).reshape(-1), want.view(np.uint16).reshape(-1)), name
+    # the permutation HuggingFace applies is undone exactly (src/tensor.rs:841-909)
+    meta = S.synth_tensor("wq", 1, cfg, 1234).astype(np.float16)
+    hf = stored[HF_NAMES["wq"].format(l=1)]
+    assert not np.array_equal(hf, meta)
+    back = huggingface_llama_model_antitranspose(hf, cfg["n_heads"])
+    assert np.array_equal(back.view(np.uint16), meta.view(np.uint16))
+    rows, cols = meta.shape
+    hd = rows // cfg["n_heads"]
+    literal = hf.reshape(cfg["n_heads"], 2, hd // 2, cols).transpose(0, 2, 1, 3).reshape(rows, cols)  # the reference's doc comment
+    assert np.array_equal(back, literal)
+    with pytest.raises(RllamaError):
+        huggingface_llama_model_antitranspose(meta[:6], 4)
+    # Meta's layout is still recognised by its params.json; anything else is unknown
+    write_llama_checkpoint(str(tmp_path / "meta"), cfg)
+    assert not DataSource.from_inferred_source(tmp_path / "meta").need_to_do_antitranspose()
+    os.makedirs(tmp_path / "empty")
+    with pytest.raises(RllamaError, match="Unknown source"):
+        DataSource.from_inferred_source(tmp_path / "empty")
+    # config.json must carry every field of the reference's struct; a corrupt archive is refused
+    import json
+    cfgp = tmp_path / "hf" / "config.json"
+    full = json.loads(cfgp.read_text())
+    del full["torch_dtype"]
+    cfgp.write_text(json.dumps(full))
+    with pytest.raises(RllamaError, match="torch_dtype"):
+        DataSource.from_vicuna_source(tmp_path / "hf")
+    full["torch_dtype"] = "float16"
+    cfgp.write_text(json.dumps(full))
+    (tmp_path / "hf" / "zzz.bin").write_bytes(b"PK\x03\x04 not really a zip")
+    with pytest.raises(RllamaError):
+        DataSource.from_vicuna_source(tmp_path / "hf")
+
+
+@pytest.mark.gpu
+def test_huggingface_checkpoint_gives_the_same_model(tmp_path, cuda_ctx):
+    from rllama_b200 import DataSettings, Transformer
+    cfg = small()
+    write_llama_checkpoint(str(tmp_path / "meta"), cfg)
+    write_hf_checkpoint(str(tmp_path / "hf"), cfg, n_files=3, deflate=True)
+    p = ModelParams.from_json(os.path.join(str(tmp_path / "hf"), "config.json"))  # serde aliases: hidden_size, ...
+    assert (p.dim, p.n_heads, p.n_layers, p.vocab_size) == (cfg["dim"], cfg["n_heads"], cfg["n_layers"], cfg["vocab"])
+    ds = DataSettings(cl=cuda_ctx).force_f16()
+    a = Transformer.from_unpickled(p.dim, p.n_layers, p.n_heads, cfg["max_seq_len"], p.norm_eps, ds, DataSource.from_inferred_source(tmp_path / "hf"))
+    b = Transformer.from_unpickled(p.dim, p.n_layers, p.n_heads, cfg["max_seq_len"], p.norm_eps, ds, DataSource.from_inferred_source(tmp_path / "meta"))
+    toks = S.synth_tokens(9, cfg["vocab"])
+    assert np.array_equal(a.forward(toks, 0, a.make_caches()), b.forward(toks, 0, b.make_caches()))
 
 
 @pytest.mark.gpu
