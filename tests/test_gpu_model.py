@@ -99,6 +99,24 @@ def test_wide_rows_one_layer(cuda_ctx, dim, heads):
     assert max(float(np.abs(a - b).max()) for a, b in zip(gl, ol)) <= F16_ABS
 
 
+@pytest.mark.parametrize("f16", [True, False])
+def test_long_context_decode(cuda_ctx, f16):
+    """More than a thousand attended positions: every attention CTA of the head's cluster walks
+    several batches of cache rows, and the prompt goes through the batched prefill path."""
+    cfg = cfg_variant("tiny", dim=256, n_heads=2, ffn=352, n_layers=1, vocab=512, max_seq_len=1100)
+    gpu, orc = build_pair(cfg, f16, cuda_ctx)
+    prompt = S.synth_tokens(1040, cfg["vocab"])
+    ot, ol = greedy_protocol(orc, prompt, 4)
+    caches = gpu.make_caches()
+    gl = [gpu.forward(prompt, 0, caches)]
+    for i, tok in enumerate(ot):
+        gl.append(gpu.forward([tok], len(prompt) + i, caches))
+    if f16:
+        assert max(float(np.abs(a - b).max()) for a, b in zip(gl, ol)) <= F16_ABS
+    else:
+        assert max(rel_err(a, b) for a, b in zip(gl, ol)) <= F32_REL
+
+
 def test_odd_head_dim_and_ffn_shapes(cuda_ctx):
     """head_dim 64 and 128, FFN widths that are not multiples of the tile sizes."""
     for over in (dict(dim=256, n_heads=2, ffn=696, n_layers=2, vocab=1000), dict(dim=384, n_heads=6, ffn=1032, n_layers=1, vocab=512)):
