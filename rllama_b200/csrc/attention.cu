@@ -506,8 +506,7 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
         }
         // same shared-memory split as the projection kernels before and after this one, so that their
         // CTAs (which prefetch weights while they wait for this kernel) can share an SM with these
-        static const bool carve = getenv("RLB_CARVE") == nullptr || atoi(getenv("RLB_CARVE")) != 0;
-        if (carve) RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         void* kargs[] = {(void*)&a};
         RLB_CUDA(cudaLaunchKernelExC(&lc, kern, kargs));
     } else if (cache_dtype == RLB_F16) {

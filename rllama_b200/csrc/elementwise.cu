@@ -300,7 +300,7 @@ int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok, co
 int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step, int32_t* tokens_out,
                           int32_t tokens_cap, const StepSync& sync) {
     static bool carve_set = false;  // keep the shared-memory split of the projection kernels around it
-    if (!carve_set && (getenv("RLB_CARVE") == nullptr || atoi(getenv("RLB_CARVE")) != 0)) {
+    if (!carve_set) {
         RLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         carve_set = true;
     }

@@ -549,8 +549,7 @@ int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         // every kernel of the decode chain asks for the same shared-memory split, so that CTAs of
         // consecutive kernels can share an SM
-        if (getenv("RLB_CARVE") == nullptr || atoi(getenv("RLB_CARVE")) != 0)
-            RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
     const int n_tiles = a.rows / RB;
