@@ -238,3 +238,55 @@ def test_inference_server_streams_json_lines(tmp_path, cuda_ctx):
         if proc.poll() is None:
             proc.kill()
             proc.wait()
+
+
+SERVER_UNIT = r'''
+#include <cstdio>
+#include "inference_server.hpp"
+int main() {
+    using namespace server;
+    const float vals[] = {1.0f, 0.5f, 0.1f, 1e-7f, 1.5e-7f, 123456.0f, 3.0e20f, 0.00001f, 0.000012f, -2.5f, 16777216.0f, 0.0f, 0.33333334f};
+    for (float v : vals) std::printf("%s\n", json_f32(v).c_str());
+    std::printf("%s\n", json_f32(0.0f / 0.0f).c_str());
+    std::printf("%s\n", json_string("a\"b\\c\n\t\x01\xc3\xa9").c_str());
+    const char* bodies[] = {
+        "{\"prompt\":\"a\\u00e9\\n\\ud83d\\ude00\",\"top_k\":3,\"temperature\":0.5,\"x\":{\"y\":[1,2,{\"z\":null}]}}",
+        " { \"prompt\" : \"p\" , \"max_seq_len\" : 7, \"max_new_tokens\":0, \"no_token_sampling\":true, \"stop_at_end_token\":false, \"top_p\":1e-1, \"repetition_penalty\": 2 } ",
+        "{\"prompt\":\"p\",\"temperature\":null,\"top_k\":null}",
+        "{\"top_k\":3}", "{\"prompt\":5}", "{\"prompt\":\"x\",\"top_k\":-1}", "{\"prompt\":\"x\",\"top_k\":1.5}", "{\"prompt\":\"x\",\"top_k\":\"3\"}",
+        "{\"prompt\":\"x\",\"no_token_sampling\":1}", "{\"prompt\":\"x\",\"prompt\":\"y\"}", "{\"prompt\":\"x\"} trailing", "[1]", "{\"prompt\":\"x\",}",
+        "{\"prompt\":\"bad \\q escape\"}", "{\"prompt\":\"\\ud83d\"}", ""};
+    for (const char* b : bodies) {
+        InferenceRequest r;
+        const bool ok = parse_request(b, &r);
+        if (!ok) { std::printf("invalid\n"); continue; }
+        std::printf("ok prompt=%s t=%g k=%llu p=%g rp=%g msl=%d:%llu mnt=%llu nts=%d stop=%d\n", json_string(r.prompt).c_str(), r.temperature,
+                    (unsigned long long)r.top_k, r.top_p, r.repetition_penalty, (int)r.has_max_seq_len, (unsigned long long)r.max_seq_len,
+                    (unsigned long long)r.max_new_tokens, (int)r.no_token_sampling, (int)r.stop_at_end_token);
+    }
+    return 0;
+}
+'''
+
+
+def test_server_request_parsing_and_json_output(tmp_path):
+    """The server's JSON reader and serde_json-style writers, compiled on their own (no device)."""
+    import shutil
+    from rllama_b200.build import HERE
+    cxx = shutil.which(os.environ.get("CXX", "g++"))
+    if cxx is None:
+        pytest.skip("no C++ compiler")
+    src = tmp_path / "unit.cpp"
+    src.write_text(SERVER_UNIT)
+    exe = tmp_path / "unit"
+    r = subprocess.run([cxx, "-std=c++17", "-Wall", "-I" + os.path.join(HERE, "cli"), str(src), "-o", str(exe), "-L" + HERE, "-lrllama_b200",
+                        "-Wl,-rpath," + HERE, "-Wl,-rpath,/usr/local/cuda/lib64", "-pthread"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = subprocess.run([str(exe)], capture_output=True, text=True).stdout.splitlines()
+    assert out[:14] == ["1.0", "0.5", "0.1", "1e-7", "1.5e-7", "123456.0", "3e20", "0.00001", "0.000012", "-2.5", "16777216.0", "0.0",
+                        "0.33333334", "null"]
+    assert out[14] == '"a\\"b\\\\c\\n\\t\\u0001é"'
+    assert out[15] == 'ok prompt="aé\\n😀" t=0.5 k=3 p=1 rp=1 msl=0:0 mnt=20 nts=0 stop=1'
+    assert out[16] == 'ok prompt="p" t=1 k=20 p=0.1 rp=2 msl=1:7 mnt=0 nts=1 stop=0'
+    assert out[17] == 'ok prompt="p" t=1 k=20 p=1 rp=1 msl=0:0 mnt=20 nts=0 stop=1'
+    assert out[18:] == ["invalid"] * 13
