@@ -227,6 +227,127 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefil
     for (int c = threadIdx.x; c < hd; c += kThreads) out[c] = cast_out<CT>(o_sh[c] / l);
 }
 
+// Prefill for head_dim 64 / 128, tiled: one CTA per (head, block of 32 query rows). Tiles of 32 cache
+// positions are staged in shared memory once (as f32) and shared by the 32 query rows, so the cache is
+// read n / 32 times instead of n times. Scores and P.V are two small f32 FMA tile products (no tensor
+// cores: q after RoPE and the softmax weights are f32 values in the reference, and rounding them to a
+// tensor-core input format would add a rounding point it does not have); the softmax runs online with a
+// running row maximum. Thread (r, g) = (tid / 8, tid % 8) owns query row r, the score columns g, g + 8,
+// g + 16, g + 24 of a tile and the output columns 4 g + 32 j ... + 3.
+constexpr int kQB = 32;   // query rows per CTA
+constexpr int kTB = 32;   // cache positions per tile
+
+template <typename CT, int HD>
+__global__ void __launch_bounds__(256) attn_prefill_tiled_kernel(const AttnPrefillArgs a) {
+    constexpr int LD = HD + 4;             // padded row stride: conflict-free float4 reads
+    constexpr int NJ = HD / 32;            // float4 output groups per thread
+    extern __shared__ __align__(16) float sm[];
+    float* q_s = sm;                       // [kQB][LD]
+    float* k_s = q_s + kQB * LD;           // [kTB][LD]
+    float* v_s = k_s + kTB * LD;           // [kTB][HD]
+    float* p_s = v_s + kTB * HD;           // [kQB][kTB + 1]
+    const int head = blockIdx.x, i0 = blockIdx.y * kQB;
+    const int tid = threadIdx.x, r = tid >> 3, g = tid & 7;
+    const int rows = min(kQB, a.n - i0);
+    for (int e = tid; e < kQB * (HD / 4); e += 256) {
+        const int rr = e / (HD / 4), c4 = e % (HD / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rr < rows) v = *reinterpret_cast<const float4*>(a.q + (int64_t)(i0 + rr) * a.q_ld + head * HD + c4 * 4);
+        *reinterpret_cast<float4*>(q_s + rr * LD + c4 * 4) = v;
+    }
+    const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * HD;
+    const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * HD;
+    const float scale = 1.0f / sqrtf((float)HD);  // src/transformer.rs:770
+    const int limit = a.start_pos + i0 + r + 1;   // row r attends to positions below this (src/tensor.rs:496-508)
+    const int t_end = a.start_pos + i0 + rows;    // the last row's limit
+    float m = -FLT_MAX, l = 0.f;
+    float4 o[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int t0 = 0; t0 < t_end; t0 += kTB) {
+        __syncthreads();  // the previous tile has been consumed (and q_s is complete)
+        for (int e = tid; e < kTB * (HD / 4); e += 256) {
+            const int tt = e / (HD / 4), c4 = e % (HD / 4);
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (t0 + tt < t_end) {
+                const CT* kp = kbase + (int64_t)(t0 + tt) * HD + c4 * 4;
+                const CT* vp = vbase + (int64_t)(t0 + tt) * HD + c4 * 4;
+                if constexpr (sizeof(CT) == 2) {
+                    const uint2 kr = *reinterpret_cast<const uint2*>(kp), vr = *reinterpret_cast<const uint2*>(vp);
+                    const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x)), k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
+                    const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
+                    kv = make_float4(k0.x, k0.y, k1.x, k1.y);
+                    vv = make_float4(v0.x, v0.y, v1.x, v1.y);
+                } else {
+                    kv = *reinterpret_cast<const float4*>(kp);
+                    vv = *reinterpret_cast<const float4*>(vp);
+                }
+            }
+            *reinterpret_cast<float4*>(k_s + tt * LD + c4 * 4) = kv;
+            *reinterpret_cast<float4*>(v_s + tt * HD + c4 * 4) = vv;
+        }
+        __syncthreads();
+        // scores of row r against the tile's positions g, g + 8, g + 16, g + 24
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+        for (int d = 0; d < HD; d += 4) {
+            const float4 qv = *reinterpret_cast<const float4*>(q_s + r * LD + d);
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float4 kv = *reinterpret_cast<const float4*>(k_s + (g + 8 * c) * LD + d);
+                s4[c] = fmaf(qv.x, kv.x, s4[c]); s4[c] = fmaf(qv.y, kv.y, s4[c]); s4[c] = fmaf(qv.z, kv.z, s4[c]); s4[c] = fmaf(qv.w, kv.w, s4[c]);
+            }
+        }
+        float tmax = -FLT_MAX;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            s4[c] = (t0 + g + 8 * c < limit) ? s4[c] * scale : -FLT_MAX;  // the causal mask
+            tmax = fmaxf(tmax, s4[c]);
+        }
+        // the eight threads of a row sit in one warp, next to each other
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+        const float m_new = fmaxf(m, tmax);
+        const float rescale = expf(m - m_new);
+        float psum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float pv = (t0 + g + 8 * c < limit) ? expf(s4[c] - m_new) : 0.f;
+            p_s[r * (kTB + 1) + g + 8 * c] = pv;
+            psum += pv;
+        }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+        l = l * rescale + psum;
+        m = m_new;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) { o[j].x *= rescale; o[j].y *= rescale; o[j].z *= rescale; o[j].w *= rescale; }
+        __syncwarp();  // a row's weights are written and read by the same warp
+#pragma unroll 4
+        for (int tt = 0; tt < kTB; tt++) {
+            const float pv = p_s[r * (kTB + 1) + tt];
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const float4 vv = *reinterpret_cast<const float4*>(v_s + tt * HD + g * 4 + 32 * j);
+                o[j].x = fmaf(pv, vv.x, o[j].x); o[j].y = fmaf(pv, vv.y, o[j].y); o[j].z = fmaf(pv, vv.z, o[j].z); o[j].w = fmaf(pv, vv.w, o[j].w);
+            }
+        }
+    }
+    if (r < rows) {
+        CT* out = reinterpret_cast<CT*>(a.out) + (int64_t)(i0 + r) * a.heads * HD + head * HD;
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int c = g * 4 + 32 * j;
+            out[c] = cast_out<CT>(o[j].x * inv); out[c + 1] = cast_out<CT>(o[j].y * inv);
+            out[c + 2] = cast_out<CT>(o[j].z * inv); out[c + 3] = cast_out<CT>(o[j].w * inv);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Decode attention, low-latency form for head_dim 64 / 128: one warp per position, online softmax.
 //
@@ -526,6 +647,19 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
     const int vec = cache_dtype == RLB_F16 ? 8 : 4;
     if (a.hd % 8 != 0 || (a.hd / 8) % vec != 0 || a.hd / vec > kThreads)
         return rlb_fail(RLB_ERR_INVALID, "attention: head_dim %d is not supported", a.hd);
+    static const bool use_tiled = getenv("RLB_ATTN_TILED") == nullptr || atoi(getenv("RLB_ATTN_TILED")) != 0;
+    if (use_tiled && a.n >= 8 && (a.hd == 64 || a.hd == 128) && a.q_ld % 4 == 0) {
+        const size_t smem = sizeof(float) * ((size_t)kQB * (a.hd + 4) + (size_t)kTB * (a.hd + 4) + (size_t)kTB * a.hd + (size_t)kQB * (kTB + 1));
+        dim3 grid(a.heads, (a.n + kQB - 1) / kQB);
+        const void* kern;
+        if (cache_dtype == RLB_F16) kern = a.hd == 128 ? (const void*)attn_prefill_tiled_kernel<__half, 128> : (const void*)attn_prefill_tiled_kernel<__half, 64>;
+        else kern = a.hd == 128 ? (const void*)attn_prefill_tiled_kernel<float, 128> : (const void*)attn_prefill_tiled_kernel<float, 64>;
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        void* kargs[] = {(void*)&a};
+        RLB_CUDA(cudaLaunchKernel(kern, grid, dim3(256), kargs, smem, ctx->stream));
+        count_launch(ctx);
+        return RLB_OK;
+    }
     const size_t smem = attn_smem_bytes(a.hd, vec, a.start_pos + a.n);
     if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "attention: %d positions do not fit in shared memory", a.start_pos + a.n);
     dim3 grid(a.heads, a.n);
