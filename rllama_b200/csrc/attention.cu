@@ -227,25 +227,27 @@ __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefil
     for (int c = threadIdx.x; c < hd; c += kThreads) out[c] = cast_out<CT>(o_sh[c] / l);
 }
 
-// Prefill for head_dim 64 / 128, tiled: one CTA per (head, block of 32 query rows). Tiles of 32 cache
-// positions are staged in shared memory once (as f32) and shared by the 32 query rows, so the cache is
-// read n / 32 times instead of n times. Scores and P.V are two small f32 FMA tile products (no tensor
+// Prefill for head_dim 64 / 128, tiled: one CTA per (head, block of 64 query rows). Tiles of 32 cache
+// positions are staged in shared memory once (as f32) and shared by the 64 query rows, so the cache is
+// read n / 64 times instead of n times. Scores and P.V are two small f32 FMA tile products (no tensor
 // cores: q after RoPE and the softmax weights are f32 values in the reference, and rounding them to a
 // tensor-core input format would add a rounding point it does not have); the softmax runs online with a
-// running row maximum. Thread (r, g) = (tid / 8, tid % 8) owns query row r, the score columns g, g + 8,
-// g + 16, g + 24 of a tile and the output columns 4 g + 32 j ... + 3.
-constexpr int kQB = 32;   // query rows per CTA
+// running row maximum. Thread (r, g) = (tid / 8, tid % 8) owns the query rows r and r + 32, the score
+// columns g, g + 8, g + 16, g + 24 of a tile and the output columns 4 g + 32 j ... + 3: every K or V
+// value read from shared memory feeds two rows (shared-memory bandwidth, not FMA rate, bounds the kernel).
+constexpr int kQB = 64;   // query rows per CTA
 constexpr int kTB = 32;   // cache positions per tile
 
 template <typename CT, int HD>
 __global__ void __launch_bounds__(256) attn_prefill_tiled_kernel(const AttnPrefillArgs a) {
     constexpr int LD = HD + 4;             // padded row stride: conflict-free float4 reads
-    constexpr int NJ = HD / 32;            // float4 output groups per thread
+    constexpr int NJ = HD / 32;            // float4 output groups per thread and row
+    constexpr int PL = kTB + 1;
     extern __shared__ __align__(16) float sm[];
     float* q_s = sm;                       // [kQB][LD]
     float* k_s = q_s + kQB * LD;           // [kTB][LD]
     float* v_s = k_s + kTB * LD;           // [kTB][HD]
-    float* p_s = v_s + kTB * HD;           // [kQB][kTB + 1]
+    float* p_s = v_s + kTB * HD;           // [kQB][PL]
     const int head = blockIdx.x, i0 = blockIdx.y * kQB;
     const int tid = threadIdx.x, r = tid >> 3, g = tid & 7;
     const int rows = min(kQB, a.n - i0);
@@ -258,12 +260,15 @@ __global__ void __launch_bounds__(256) attn_prefill_tiled_kernel(const AttnPrefi
     const CT* kbase = reinterpret_cast<const CT*>(a.kcache) + (int64_t)head * a.max_seq * HD;
     const CT* vbase = reinterpret_cast<const CT*>(a.vcache) + (int64_t)head * a.max_seq * HD;
     const float scale = 1.0f / sqrtf((float)HD);  // src/transformer.rs:770
-    const int limit = a.start_pos + i0 + r + 1;   // row r attends to positions below this (src/tensor.rs:496-508)
+    // row r + 32 h attends to the positions below limit[h] (src/tensor.rs:496-508)
+    const int limit[2] = {a.start_pos + i0 + r + 1, a.start_pos + i0 + r + 33};
     const int t_end = a.start_pos + i0 + rows;    // the last row's limit
-    float m = -FLT_MAX, l = 0.f;
-    float4 o[NJ];
+    float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
+    float4 o[2][NJ];
 #pragma unroll
-    for (int j = 0; j < NJ; j++) o[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int j = 0; j < NJ; j++) o[h][j] = make_float4(0.f, 0.f, 0.f, 0.f);
 
     for (int t0 = 0; t0 < t_end; t0 += kTB) {
         __syncthreads();  // the previous tile has been consumed (and q_s is complete)
@@ -288,62 +293,72 @@ __global__ void __launch_bounds__(256) attn_prefill_tiled_kernel(const AttnPrefi
             *reinterpret_cast<float4*>(v_s + tt * HD + c4 * 4) = vv;
         }
         __syncthreads();
-        // scores of row r against the tile's positions g, g + 8, g + 16, g + 24
-        float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
+        // scores of rows r, r + 32 against the tile's positions g, g + 8, g + 16, g + 24
+        float s4[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
         for (int d = 0; d < HD; d += 4) {
-            const float4 qv = *reinterpret_cast<const float4*>(q_s + r * LD + d);
+            const float4 q0 = *reinterpret_cast<const float4*>(q_s + r * LD + d);
+            const float4 q1 = *reinterpret_cast<const float4*>(q_s + (r + 32) * LD + d);
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 const float4 kv = *reinterpret_cast<const float4*>(k_s + (g + 8 * c) * LD + d);
-                s4[c] = fmaf(qv.x, kv.x, s4[c]); s4[c] = fmaf(qv.y, kv.y, s4[c]); s4[c] = fmaf(qv.z, kv.z, s4[c]); s4[c] = fmaf(qv.w, kv.w, s4[c]);
+                s4[0][c] = fmaf(q0.x, kv.x, s4[0][c]); s4[0][c] = fmaf(q0.y, kv.y, s4[0][c]); s4[0][c] = fmaf(q0.z, kv.z, s4[0][c]); s4[0][c] = fmaf(q0.w, kv.w, s4[0][c]);
+                s4[1][c] = fmaf(q1.x, kv.x, s4[1][c]); s4[1][c] = fmaf(q1.y, kv.y, s4[1][c]); s4[1][c] = fmaf(q1.z, kv.z, s4[1][c]); s4[1][c] = fmaf(q1.w, kv.w, s4[1][c]);
             }
         }
-        float tmax = -FLT_MAX;
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            s4[c] = (t0 + g + 8 * c < limit) ? s4[c] * scale : -FLT_MAX;  // the causal mask
-            tmax = fmaxf(tmax, s4[c]);
+        for (int h = 0; h < 2; h++) {
+            float tmax = -FLT_MAX;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                s4[h][c] = (t0 + g + 8 * c < limit[h]) ? s4[h][c] * scale : -FLT_MAX;  // the causal mask
+                tmax = fmaxf(tmax, s4[h][c]);
+            }
+            // the eight threads of a row sit in one warp, next to each other
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            const float m_new = fmaxf(m[h], tmax);
+            const float rescale = expf(m[h] - m_new);
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const float pv = (t0 + g + 8 * c < limit[h]) ? expf(s4[h][c] - m_new) : 0.f;
+                p_s[(r + 32 * h) * PL + g + 8 * c] = pv;
+                psum += pv;
+            }
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+            l[h] = l[h] * rescale + psum;
+            m[h] = m_new;
+#pragma unroll
+            for (int j = 0; j < NJ; j++) { o[h][j].x *= rescale; o[h][j].y *= rescale; o[h][j].z *= rescale; o[h][j].w *= rescale; }
         }
-        // the eight threads of a row sit in one warp, next to each other
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
-        const float m_new = fmaxf(m, tmax);
-        const float rescale = expf(m - m_new);
-        float psum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const float pv = (t0 + g + 8 * c < limit) ? expf(s4[c] - m_new) : 0.f;
-            p_s[r * (kTB + 1) + g + 8 * c] = pv;
-            psum += pv;
-        }
-        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 4);
-        l = l * rescale + psum;
-        m = m_new;
-#pragma unroll
-        for (int j = 0; j < NJ; j++) { o[j].x *= rescale; o[j].y *= rescale; o[j].z *= rescale; o[j].w *= rescale; }
         __syncwarp();  // a row's weights are written and read by the same warp
 #pragma unroll 4
         for (int tt = 0; tt < kTB; tt++) {
-            const float pv = p_s[r * (kTB + 1) + tt];
+            const float p0 = p_s[r * PL + tt], p1 = p_s[(r + 32) * PL + tt];
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const float4 vv = *reinterpret_cast<const float4*>(v_s + tt * HD + g * 4 + 32 * j);
-                o[j].x = fmaf(pv, vv.x, o[j].x); o[j].y = fmaf(pv, vv.y, o[j].y); o[j].z = fmaf(pv, vv.z, o[j].z); o[j].w = fmaf(pv, vv.w, o[j].w);
+                o[0][j].x = fmaf(p0, vv.x, o[0][j].x); o[0][j].y = fmaf(p0, vv.y, o[0][j].y); o[0][j].z = fmaf(p0, vv.z, o[0][j].z); o[0][j].w = fmaf(p0, vv.w, o[0][j].w);
+                o[1][j].x = fmaf(p1, vv.x, o[1][j].x); o[1][j].y = fmaf(p1, vv.y, o[1][j].y); o[1][j].z = fmaf(p1, vv.z, o[1][j].z); o[1][j].w = fmaf(p1, vv.w, o[1][j].w);
             }
         }
     }
-    if (r < rows) {
-        CT* out = reinterpret_cast<CT*>(a.out) + (int64_t)(i0 + r) * a.heads * HD + head * HD;
-        const float inv = 1.0f / l;
 #pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            const int c = g * 4 + 32 * j;
-            out[c] = cast_out<CT>(o[j].x * inv); out[c + 1] = cast_out<CT>(o[j].y * inv);
-            out[c + 2] = cast_out<CT>(o[j].z * inv); out[c + 3] = cast_out<CT>(o[j].w * inv);
+    for (int h = 0; h < 2; h++) {
+        const int rr = r + 32 * h;
+        if (rr < rows) {
+            CT* out = reinterpret_cast<CT*>(a.out) + (int64_t)(i0 + rr) * a.heads * HD + head * HD;
+            const float inv = 1.0f / l[h];
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const int c = g * 4 + 32 * j;
+                out[c] = cast_out<CT>(o[h][j].x * inv); out[c + 1] = cast_out<CT>(o[h][j].y * inv);
+                out[c + 2] = cast_out<CT>(o[h][j].z * inv); out[c + 3] = cast_out<CT>(o[h][j].w * inv);
+            }
         }
     }
 }
