@@ -189,6 +189,30 @@ def workload_name(cfg):
         cfg["name"], "f16" if cfg["f16"] else "f32", cfg["prompt"], cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"])
 
 
+def gemm_sweep():
+    """Prefill contraction alone: out[n][M] = X[n][K] . W[M][K]^T through the tier-1 op, 20 calls per
+    shape bracketed by a flush of the library's stream (wall clock; the calls are back to back)."""
+    from rllama_b200 import F16, Cuda
+    cl = Cuda(verbose=False, nth_device=0)
+    rng = np.random.default_rng(0)
+    for n in (128, 512, 1024, 2048):
+        for (M, K) in ((12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (3072, 8192), (8192, 1024)):
+            W = cl.upload(rng.normal(0, 0.02, size=(M, K)).astype(np.float16))
+            X = cl.upload(rng.normal(0, 1.0, size=(n, K)).astype(np.float16))
+            out = cl.zeros(n, M, F16)
+            for _ in range(3):
+                out.matrix_mul_inplace_transposed(X, W)
+            cl.flush()
+            t = time.perf_counter()
+            for _ in range(20):
+                out.matrix_mul_inplace_transposed(X, W)
+            cl.flush()
+            dt = (time.perf_counter() - t) / 20
+            print(json.dumps({"rows": n, "M": M, "K": K, "us": round(dt * 1e6, 1), "tflops": round(2.0 * n * M * K / dt / 1e12, 1),
+                              "weight_gbs": round(M * K * 2 / dt / 1e9, 1)}), flush=True)
+            W.free(); X.free(); out.free()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -200,7 +224,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-kernels", action="store_true", help="also time each kernel class with events (eager, untimed extra pass)")
+    ap.add_argument("--gemm-sweep", action="store_true",
+                    help="time the prefill GEMM (rlb_matrix_mul_inplace_transposed, f16) over prompt lengths and layer shapes, then exit")
     args = ap.parse_args()
+    if args.gemm_sweep:
+        return gemm_sweep()
 
     cfg = dict(S.CONFIGS[args.workload]); cfg["name"] = args.workload
     if args.layers:
