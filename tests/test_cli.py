@@ -214,6 +214,17 @@ def test_inference_server_streams_json_lines(tmp_path, cuda_ctx):
         for i in (0, 1, 2, 13, 57, 399):
             assert abs(allp[tk.id_to_str(i)]["p"] - float(first_logits[i])) <= 1e-6 * max(1.0, abs(float(first_logits[i])))
         assert allp["</s>"].get("is_end_token") is True and "is_end_token" not in allp["<s>"]
+        # several requests at once: each has its own caches, the device work is serialised inside the library
+        import threading
+        results = [None] * 4
+        def post(i):
+            results[i] = _post(port, path, json.dumps({"prompt": prompt, "top_k": 1, "max_new_tokens": 6}))
+        threads = [threading.Thread(target=post, args=(i,)) for i in range(4)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        assert all(r == (200, body) for r in results)
         # the reference's refusals
         for bad, text in (("{not json", "Invalid JSON."), (json.dumps({"top_k": 3}), "Invalid JSON."), (json.dumps({"prompt": 5}), "Invalid JSON."),
                           (json.dumps({"prompt": "x", "top_k": -1}), "Invalid JSON."), (json.dumps({"prompt": "x", "top_k": 1.5}), "Invalid JSON."),
