@@ -111,6 +111,24 @@ def test_cli_generates_the_same_text_as_the_python_chain(tmp_path, cuda_ctx):
     assert r.returncode == 0 and r.stdout == prompt + text + "\n"
     r = run_cli(["--model-path", str(tmp_path / "nowhere")] + args[2:])
     assert r.returncode == 1 and r.stderr.startswith("Error: ")
+    # interactive mode (src/rllama_main.rs:824-838, :886-893): the system prompt, then a line from stdin wrapped in
+    # prefix / postfix and fed token by token, generation until the sequence is full; a second read at end of input
+    # yields an empty line
+    iargs = [x for x in args if x not in ("--prompt", prompt)] + ["--start-interactive", "--interactive-system-prompt", "kalo miren",
+                                                                  "--interactive-prompt-prefix", " ", "--interactive-prompt-postfix", " vu",
+                                                                  "--interactive-stop", "zéñu"]
+    r = run_cli(iargs, stdin="ren tas\n")
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.startswith("kalo miren") and " ren tas vu" in r.stdout
+    sys_toks = tk.tokenize_to_ids("kalo miren")
+    user_toks = tk.tokenize_to_ids(" ren tas vu")[1:]
+    assert len(sys_toks) + len(user_toks) < max_seq
+    r2 = run_cli(iargs, {"CLICOLOR_FORCE": "1"}, stdin="ren tas\n")
+    out2 = ANSI.sub("", r2.stdout)
+    assert 'Interactive mode stop token sequences: ["zéñu"]' in out2 and "System prompt:\n  kalo miren" in out2
+    assert "Interactive prompt prefix:  \nInteractive prompt postfix:  vu" in out2
+    r = run_cli(iargs + ["--prompt", "x"], stdin="")
+    assert r.returncode == 1 and "Cannot start interactive mode with a prompt." in r.stderr
 
 
 def _free_port():
