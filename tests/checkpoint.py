@@ -99,7 +99,7 @@ def hf_permute(w, n_heads):
     return np.ascontiguousarray(w.reshape(n_heads, hd // 2, 2, cols).transpose(0, 2, 1, 3).reshape(rows, cols))
 
 
-def write_hf_checkpoint(path, cfg, seed=1234, n_files=2, deflate=False):
+def write_hf_checkpoint(path, cfg, seed=1234, n_files=2, deflate=False, zip64=False):
     """A HuggingFace-style directory (config.json, pytorch_model.bin.index.json, *.bin torch.save
     archives) holding the same synthetic weights as write_llama_checkpoint, with HuggingFace's tensor
     names and its q/k row permutation. Returns {hf name: float16 array as stored}."""
@@ -127,7 +127,11 @@ def write_hf_checkpoint(path, cfg, seed=1234, n_files=2, deflate=False):
             out = io.BytesIO()
             with zipfile.ZipFile(io.BytesIO(raw)) as zin, zipfile.ZipFile(out, "w", zipfile.ZIP_DEFLATED) as zout:
                 for info in zin.infolist():
-                    zout.writestr(info.filename, zin.read(info))
+                    if zip64:  # zip64 extra fields in the local header and the central directory
+                        with zout.open(info.filename, "w", force_zip64=True) as dst:
+                            dst.write(zin.read(info))
+                    else:
+                        zout.writestr(info.filename, zin.read(info))
             raw = out.getvalue()
         with open(os.path.join(path, fname), "wb") as f:
             f.write(raw)

@@ -79,12 +79,12 @@ def test_loader_errors(tmp_path):
         DataSource.from_llama_source(tmp_path / "junk")
 
 
-@pytest.mark.parametrize("deflate", [False, True])
-def test_huggingface_source_reads_archives_in_place(tmp_path, deflate):
+@pytest.mark.parametrize("deflate,zip64", [(False, False), (True, False), (True, True)])
+def test_huggingface_source_reads_archives_in_place(tmp_path, deflate, zip64):
     """DataSource::from_vicuna_source / from_inferred_source and the q/k anti-transpose."""
     from rllama_b200.data_source import huggingface_llama_model_antitranspose
     cfg = small()
-    stored = write_hf_checkpoint(str(tmp_path / "hf"), cfg, n_files=2, deflate=deflate)
+    stored = write_hf_checkpoint(str(tmp_path / "hf"), cfg, n_files=2, deflate=deflate, zip64=zip64)
     ds = DataSource.from_inferred_source(tmp_path / "hf")
     assert ds.need_to_do_antitranspose() and ds.shards() == 1
     for name, want in stored.items():
