@@ -149,7 +149,7 @@ def test_single_token_prompt_and_last_position(cuda_ctx):
 
 
 def test_prefill_equals_token_by_token_and_chunked(cuda_ctx):
-    cfg = cfg_variant("tiny", n_layers=2, vocab=2000)
+    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, max_seq_len=160)
     gpu, _ = build_pair(cfg, False, cuda_ctx, with_oracle=False)
     toks = S.synth_tokens(11, cfg["vocab"])
     full = gpu.forward(toks, 0, gpu.make_caches())
@@ -162,6 +162,17 @@ def test_prefill_equals_token_by_token_and_chunked(cuda_ctx):
     gpu.forward(toks[:4], 0, c2)
     chunked = gpu.forward(toks[4:], 4, c2)
     assert rel_err(chunked, full) <= F32_REL
+    # chunks long enough for the tiled attention kernel, the second one at start_pos > 0 and across its
+    # 64-row blocks
+    long_toks = S.synth_tokens(150, cfg["vocab"])
+    c3 = gpu.make_caches()
+    full3 = gpu.forward(long_toks, 0, c3)
+    c4 = gpu.make_caches()
+    gpu.forward(long_toks[:37], 0, c4)
+    chunked3 = gpu.forward(long_toks[37:], 37, c4)
+    assert rel_err(chunked3, full3) <= F32_REL
+    k_full, k_chunk = c3.read("k", 1, 3, 149), c4.read("k", 1, 3, 149)
+    assert np.array_equal(k_full, k_chunk)
 
 
 def test_device_greedy_loop_equals_host_loop(cuda_ctx):
