@@ -224,6 +224,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile-kernels", action="store_true", help="also time each kernel class with events (eager, untimed extra pass)")
+    ap.add_argument("--f32", action="store_true", help="keep the weights and caches in f32 (the reference without --f16)")
     ap.add_argument("--gemm-sweep", action="store_true",
                     help="time the prefill GEMM (rlb_matrix_mul_inplace_transposed, f16) over prompt lengths and layer shapes, then exit")
     args = ap.parse_args()
@@ -231,6 +232,8 @@ def main():
         return gemm_sweep()
 
     cfg = dict(S.CONFIGS[args.workload]); cfg["name"] = args.workload
+    if args.f32:
+        cfg["f16"] = False
     if args.layers:
         cfg["n_layers"] = args.layers
     rank = int(os.environ.get("RANK", "0"))
