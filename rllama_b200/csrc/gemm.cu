@@ -86,9 +86,13 @@ __global__ void __launch_bounds__(256) gemm_nt_kernel(const T* __restrict__ A, i
 }  // namespace
 
 int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, float* C, int64_t ldc, int n,
-                   int M, int K, int round_out, int* err) {
+                   int M, int K, int round_out, int* err, int w_f16_exact) {
     if (dtype == RLB_F16 && tc_enabled() && n >= kTcMinRows && gemm_tc_supported(A, lda, W, ldw, n, M, K))
         return launch_gemm_tc_f32out(ctx, A, lda, W, ldw, C, ldc, n, M, K, round_out, err ? err : ctx->d_err);
+    static const bool tf32x2 = getenv("RLB_GEMM_TF32X2") == nullptr || atoi(getenv("RLB_GEMM_TF32X2")) != 0;
+    if (dtype == RLB_F32 && w_f16_exact && !round_out && tf32x2 && tc_enabled() && n >= kTcMinRows &&
+        gemm_tc_f32_supported(A, lda, W, ldw, n, M, K))
+        return launch_gemm_tc_f32w(ctx, A, lda, W, ldw, C, ldc, n, M, K, err ? err : ctx->d_err);
     dim3 grid((M + BN - 1) / BN, (n + BM - 1) / BM);
     if (grid.y > 65535) return rlb_fail(RLB_ERR_LIMIT, "gemm: too many rows (%d)", n);
     if (dtype == RLB_F16) {

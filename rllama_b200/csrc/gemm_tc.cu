@@ -85,6 +85,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -96,11 +102,21 @@ template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return
 // blockIdx.z selects a K range (split-K): with more than one split every split stores its f32
 // partial tile into its own [n][ldc] slab of C (slab stride `split_stride` elements) and a second
 // kernel adds the slabs in a fixed order, so the result does not depend on timing.
-template <int BN, typename OT>
+//
+// TF32 = true is the f32 form for weights whose values are f16-representable (what the checkpoint
+// loader produces): operands are 32-bit, kind::tf32, 32 K columns (still 128 bytes) per stage. A weight
+// with at most 11 significant bits is exact in TF32; the activations are not, so the caller passes them
+// split into x = hi + lo (hi = x rounded to TF32, lo = x - hi) and every k-block is multiplied twice,
+// W x hi and W x lo, into the same accumulator: all products are exact in f32 and what is dropped of lo is
+// below 2^-21 of x.
+template <int BN, typename OT, bool TF32>
 __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                             const __grid_constant__ CUtensorMap tm_x, OT* __restrict__ C, int64_t ldc,
+                                                             const __grid_constant__ CUtensorMap tm_x,
+                                                             const __grid_constant__ CUtensorMap tm_x2, OT* __restrict__ C, int64_t ldc,
                                                              int n, int Mrows, int K, int round_out, int64_t split_stride, int* err) {
     constexpr int kStages = stages_for(BN);
+    constexpr int BKE = TF32 ? BK / 2 : BK;   // K columns of a stage (128 bytes either way)
+    constexpr int PASSES = TF32 ? 2 : 1;
     constexpr uint32_t A_BYTES = BM * BK * 2;
     constexpr uint32_t B_BYTES = BN * BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -118,7 +134,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM;  // first weight row of the tile
     const int n0 = blockIdx.y * BN;  // first token of the tile
-    const int nkb_total = (K + BK - 1) / BK;
+    const int nkb_total = (K + BKE - 1) / BKE;
     const int per_split = (nkb_total + (int)gridDim.z - 1) / (int)gridDim.z;
     const int kb_first = (int)blockIdx.z * per_split;
     const int nkb = max(0, min(nkb_total, kb_first + per_split) - kb_first);  // k-blocks of this split
@@ -146,21 +162,23 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
-        for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % kStages;
-            const uint32_t ph = (kb / kStages) & 1u;
+        for (int it = 0; it < nkb * PASSES; it++) {
+            const int s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            const int kb = it / PASSES;
             if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
             unsigned char* a_s = tiles + (size_t)s * STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a_s, &tm_w, (kb_first + kb) * BK, m0, &full_bar[s]);
-            tma_load_2d(a_s + A_BYTES, &tm_x, (kb_first + kb) * BK, n0, &full_bar[s]);
+            tma_load_2d(a_s, &tm_w, (kb_first + kb) * BKE, m0, &full_bar[s]);  // (second pass: the same tile again, from L2)
+            tma_load_2d(a_s + A_BYTES, (PASSES == 2 && (it & 1)) ? &tm_x2 : &tm_x, (kb_first + kb) * BKE, n0, &full_bar[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
         // instruction descriptor: f32 accumulator, f16 A and B, both K-major, N = BN, M = 128
-        const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        // (operand format field: 0 = f16, 2 = tf32, for A at bit 7 and B at bit 10)
+        const uint32_t idesc = (1u << 4) | (TF32 ? ((2u << 7) | (2u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         bool ok = true;
-        for (int kb = 0; kb < nkb && ok; kb++) {
+        for (int kb = 0; kb < nkb * PASSES && ok; kb++) {
             const int s = kb % kStages;
             const uint32_t ph = (kb / kStages) & 1u;
             ok = mbar_wait(&full_bar[s], ph, dead, err);
@@ -170,8 +188,9 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
             for (int k = 0; k < BK / 16; k++) {
-                // 16 K columns = 32 bytes further along the swizzled row
-                umma_f16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+                // one instruction covers 32 bytes of K (16 f16 or 8 tf32 columns) along the swizzled row
+                if (TF32) umma_tf32(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+                else umma_f16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit(&empty_bar[s]);  // the slot is free once these MMAs have read it
         }
@@ -243,25 +262,28 @@ int load_encode() {
     return RLB_OK;
 }
 
-// f16 row-major [rows][K] with row stride ld elements; box = 64 columns x box_rows rows, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
+// Row-major [rows][K] (f16, or f32 when `f32`) with row stride ld elements; box = 128 bytes of columns x
+// box_rows rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows, bool f32 = false) {
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
+    cuuint32_t box[2] = {(cuuint32_t)(f32 ? BK / 2 : BK), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    CUresult r = g_encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return rlb_fail(RLB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return RLB_OK;
 }
 
-template <int BN, typename OT>
-int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, OT* C, int64_t ldc, int n, int M, int K, int round_out, int* err) {
+// scratch_off: bytes of the context's GEMM scratch the caller already uses (the split activations).
+template <int BN, typename OT, bool TF32>
+int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tx2, OT* C, int64_t ldc, int n, int M, int K,
+              int round_out, int* err, size_t scratch_off) {
     const size_t smem = (size_t)stages_for(BN) * (BM * BK * 2 + BN * BK * 2) + 1024;
     dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN, 1);
     // few tiles: split K so that most SMs stream weights
-    const int tiles = (int)(grid.x * grid.y), nkb = (K + BK - 1) / BK;
+    const int tiles = (int)(grid.x * grid.y), nkb = (K + BK - 1) / BK * (TF32 ? 2 : 1);
     int splits = 1;
     if (tiles * 5 < ctx->sm_count * 3) {
         splits = (ctx->sm_count + tiles - 1) / tiles;
@@ -269,37 +291,29 @@ int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, OT* C,
         while (splits > 1 && nkb / splits < 8) splits--;
     }
     if (splits == 1) {
-        auto kern = gemm_tc_kernel<BN, OT>;
+        auto kern = gemm_tc_kernel<BN, OT, TF32>;
         static bool set = false;
         if (!set) {
             RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set = true;
         }
-        kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, C, ldc, n, M, K, round_out, 0, err);
+        kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, C, ldc, n, M, K, round_out, 0, err);
         RLB_LAUNCH_CHECK();
         count_launch(ctx);
         return RLB_OK;
     }
     // slabs of f32 partial tiles in the context's scratch
-    const size_t need = (size_t)splits * n * M * sizeof(float);
-    if (need > ctx->gemm_scratch_bytes) {
-        RLB_CUDA(cudaStreamSynchronize(ctx->stream));
-        if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
-        ctx->gemm_scratch = nullptr;
-        ctx->gemm_scratch_bytes = 0;
-        cudaError_t e = cudaMalloc(&ctx->gemm_scratch, need);
-        if (e != cudaSuccess) return rlb_fail(RLB_ERR_OOM, "split-K scratch (%zu bytes): %s", need, cudaGetErrorString(e));
-        ctx->gemm_scratch_bytes = need;
-    }
-    float* part = static_cast<float*>(ctx->gemm_scratch);
-    auto kern = gemm_tc_kernel<BN, float>;
+    const size_t need = scratch_off + (size_t)splits * n * M * sizeof(float);
+    if (need > ctx->gemm_scratch_bytes) return rlb_fail(RLB_ERR_STATE, "gemm: scratch of %zu bytes was not reserved", need);
+    float* part = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + scratch_off);
+    auto kern = gemm_tc_kernel<BN, float, TF32>;
     static bool set = false;
     if (!set) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
     grid.z = splits;
-    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, part, (int64_t)M, n, M, K, 0, (int64_t)n * M, err);
+    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, part, (int64_t)M, n, M, K, 0, (int64_t)n * M, err);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     const int64_t total = (int64_t)n * M;
@@ -311,19 +325,63 @@ int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, OT* C,
     return RLB_OK;
 }
 
-template <typename OT>
+// Grows the context's GEMM scratch (split activations + split-K slabs) to at least `need` bytes.
+int reserve_scratch(rlb_ctx* ctx, size_t need) {
+    if (need <= ctx->gemm_scratch_bytes) return RLB_OK;
+    RLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->gemm_scratch) cudaFree(ctx->gemm_scratch);
+    ctx->gemm_scratch = nullptr;
+    ctx->gemm_scratch_bytes = 0;
+    cudaError_t e = cudaMalloc(&ctx->gemm_scratch, need);
+    if (e != cudaSuccess) return rlb_fail(RLB_ERR_OOM, "GEMM scratch (%zu bytes): %s", need, cudaGetErrorString(e));
+    ctx->gemm_scratch_bytes = need;
+    return RLB_OK;
+}
+
+// hi = x rounded to TF32 (10 explicit mantissa bits), lo = x - hi (exact in f32)
+__global__ void tf32_split_kernel(const float* __restrict__ x, int64_t ldx, int n, int K, float* __restrict__ hi, float* __restrict__ lo) {
+    const int64_t total = (int64_t)n * K;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / K, c = i - r * K;
+        const float v = x[r * ldx + c];
+        uint32_t h;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+        const float hv = __uint_as_float(h);
+        hi[i] = hv;
+        lo[i] = v - hv;
+    }
+}
+
+template <typename OT, bool TF32>
 int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
               int* err) {
     RLB_TRY(load_encode());
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
-    CUtensorMap tw, tx;
-    RLB_TRY(make_map(&tw, W, M, K, ldw, BM));
-    RLB_TRY(make_map(&tx, X, n, K, ldx, bn));
+    // scratch: [x hi | x lo] for the f32 form, then up to 8 split-K slabs
+    const size_t xs = TF32 ? (((size_t)n * K * sizeof(float) + 255) & ~(size_t)255) : 0;
+    RLB_TRY(reserve_scratch(ctx, 2 * xs + (size_t)8 * n * M * sizeof(float)));
+    CUtensorMap tw, tx, tx2;
+    RLB_TRY(make_map(&tw, W, M, K, ldw, BM, TF32));
+    if (TF32) {
+        float* hi = static_cast<float*>(ctx->gemm_scratch);
+        float* lo = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + xs);
+        const int64_t total = (int64_t)n * K;
+        int g = (int)((total + 255) / 256);
+        if (g > ctx->sm_count * 16) g = ctx->sm_count * 16;
+        tf32_split_kernel<<<g, 256, 0, ctx->stream>>>(static_cast<const float*>(X), ldx, n, K, hi, lo);
+        RLB_LAUNCH_CHECK();
+        count_launch(ctx);
+        RLB_TRY(make_map(&tx, hi, n, K, K, bn, true));
+        RLB_TRY(make_map(&tx2, lo, n, K, K, bn, true));
+    } else {
+        RLB_TRY(make_map(&tx, X, n, K, ldx, bn));
+        tx2 = tx;
+    }
     switch (bn) {
-        case 256: return launch_bn<256, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
-        case 128: return launch_bn<128, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
-        case 64: return launch_bn<64, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
-        default: return launch_bn<32, OT>(ctx, tw, tx, C, ldc, n, M, K, round_out, err);
+        case 256: return launch_bn<256, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
+        case 128: return launch_bn<128, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
+        case 64: return launch_bn<64, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
+        default: return launch_bn<32, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
     }
 }
 
@@ -339,10 +397,23 @@ bool gemm_tc_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, i
 
 int launch_gemm_tc_f32out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M, int K,
                           int round_out, int* err) {
-    return launch_tc<float>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    return launch_tc<float, false>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
 }
 
 int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, void* C, int64_t ldc, int n, int M, int K,
                           int* err) {
-    return launch_tc<__half>(ctx, X, ldx, W, ldw, reinterpret_cast<__half*>(C), ldc, n, M, K, 0, err);
+    return launch_tc<__half, false>(ctx, X, ldx, W, ldw, reinterpret_cast<__half*>(C), ldc, n, M, K, 0, err);
+}
+
+// f32 operands, weights known to hold f16-representable values: two TF32 passes (see the kernel).
+bool gemm_tc_f32_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, int n, int M, int K) {
+    if (n < 1 || M < 1 || K < 8 || K % 4 != 0) return false;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
+    if ((ldx * 4) % 16 != 0 || (ldw * 4) % 16 != 0) return false;
+    return true;
+}
+
+int launch_gemm_tc_f32w(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M, int K,
+                        int* err) {
+    return launch_tc<float, true>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, 0, err);
 }

@@ -268,13 +268,18 @@ int launch_cache_shift_left(rlb_ctx* ctx, void* cache, rlb_dtype dtype, int64_t 
 // ---------------------------------------------------------------------------------------
 // err: device-visible error word for the tensor-core path (nullptr: the context's word).
 int launch_gemm_nt(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, float* C,
-                   int64_t ldc, int n, int M, int K, int round_out, int* err = nullptr);
+                   int64_t ldc, int n, int M, int K, int round_out, int* err = nullptr, int w_f16_exact = 0);
+// (w_f16_exact: the f32 weights hold f16-representable values, so the two-pass TF32 tensor-core form is exact enough)
 // Same contraction, output stored in the operand dtype (tier-1 op).
 int launch_gemm_nt_typed(rlb_ctx* ctx, rlb_dtype dtype, const void* A, int64_t lda, const void* W, int64_t ldw, void* C,
                          int64_t ldc, int n, int M, int K);
 
 // tcgen05 tile kernel for f16 operands (gemm_tc.cu)
 bool gemm_tc_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, int n, int M, int K);
+// f32 operands whose weights hold f16-representable values (two TF32 passes over activations split into hi + lo)
+bool gemm_tc_f32_supported(const void* X, int64_t ldx, const void* W, int64_t ldw, int n, int M, int K);
+int launch_gemm_tc_f32w(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M, int K,
+                        int* err);
 int launch_gemm_tc_f32out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, float* C, int64_t ldc, int n, int M,
                           int K, int round_out, int* err);
 int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, void* C, int64_t ldc, int n, int M,

@@ -107,6 +107,7 @@ struct rlb_model {
     uint64_t graph_gen = 0;          // bumped when captured graphs become stale
 
     // options / statistics
+    bool w_f16_exact = true;  // every projection matrix arrived as f16 (or was checked): its f32 copy is exact in TF32
     bool use_graph = true;
     bool use_mega = false;   // one persistent kernel per decoded token (decode_mega.cu); off by default: the
                              // chain of dependent-launch kernels is faster (3.8 against 2.6 ms per 7B token when both were measured)
@@ -513,21 +514,21 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         char* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.attn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         // q, k and v in one GEMM: row i of the result is [q_i | k_i | v_i]
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.wqkv, d, m->pf_qkv, 3 * nq, n, 3 * nq, d, f16, m->scalars + 8));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.wqkv, d, m->pf_qkv, 3 * nq, n, 3 * nq, d, f16, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(launch_rope_append(ctx, m->pf_qkv, m->pf_qkv + nq, m->pf_qkv + 2 * nq, 3 * nq, n, start_pos, m->nh, m->hd,
                                    m->p.max_seq_len, m->rope, m->wdt, kc, vc));
         AttnPrefillArgs aa;
         aa.q = m->pf_qkv; aa.q_ld = 3 * nq; aa.kcache = kc; aa.vcache = vc; aa.out = m->pf_o; aa.n = n; aa.start_pos = start_pos;
         aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len;
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         // w1 and w3 (stored back to back) in one GEMM: row i of the result is [w1 x_i | w3 x_i]
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, 2 * F, n, 2 * F, d, f16, m->scalars + 8));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, 2 * F, n, 2 * F, d, f16, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g1 + F, 2 * F, n, F, m->wdt, m->pf_g));
-        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj, m->scalars + 8));
+        RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
         RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
     }
@@ -694,6 +695,8 @@ int rlb_model_set_tensor(rlb_model* m, rlb_tensor_kind kind, int32_t layer, cons
     int64_t r0 = 0, nr = 0, c0 = 0, nc = 0;  // slice kept by this rank
     void* dst = nullptr; int64_t dst_ld = 0; rlb_dtype ddt = m->wdt;
     LayerW* W = per_layer ? &m->L[layer] : nullptr;
+    // f32 data may carry more than f16's 11 significant bits: the prefill then keeps the exact f32 FMA GEMM
+    if (kind >= RLB_WQ && kind <= RLB_W3 && dtype == RLB_F32) m->w_f16_exact = false;
     switch (kind) {
         case RLB_TOK_EMBEDDINGS: er = Vv; ec = d; nr = Vv; nc = d; dst = m->tok_emb; dst_ld = d; ddt = RLB_F32; break;
         case RLB_OUTPUT: er = Vv; ec = d; r0 = m->v0; nr = m->V; nc = d; dst = m->output; dst_ld = d; ddt = RLB_F32; break;
