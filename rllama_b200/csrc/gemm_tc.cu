@@ -276,20 +276,24 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int
     return RLB_OK;
 }
 
-// scratch_off: bytes of the context's GEMM scratch the caller already uses (the split activations).
-template <int BN, typename OT, bool TF32>
-int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tx2, OT* C, int64_t ldc, int n, int M, int K,
-              int round_out, int* err, size_t scratch_off) {
-    const size_t smem = (size_t)stages_for(BN) * (BM * BK * 2 + BN * BK * 2) + 1024;
-    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN, 1);
-    // few tiles: split K so that most SMs stream weights
-    const int tiles = (int)(grid.x * grid.y), nkb = (K + BK - 1) / BK * (TF32 ? 2 : 1);
+// Few output tiles: split K so that most SMs stream weights.
+int pick_splits(const rlb_ctx* ctx, int tiles, int nkb) {
     int splits = 1;
     if (tiles * 5 < ctx->sm_count * 3) {
         splits = (ctx->sm_count + tiles - 1) / tiles;
         if (splits > 8) splits = 8;
         while (splits > 1 && nkb / splits < 8) splits--;
     }
+    return splits;
+}
+
+// scratch_off: bytes of the context's GEMM scratch the caller already uses (the split activations).
+template <int BN, typename OT, bool TF32>
+int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tx2, OT* C, int64_t ldc, int n, int M, int K,
+              int round_out, int* err, size_t scratch_off) {
+    const size_t smem = (size_t)stages_for(BN) * (BM * BK * 2 + BN * BK * 2) + 1024;
+    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN, 1);
+    const int splits = pick_splits(ctx, (int)(grid.x * grid.y), (K + BK - 1) / BK * (TF32 ? 2 : 1));
     if (splits == 1) {
         auto kern = gemm_tc_kernel<BN, OT, TF32>;
         static bool set = false;
@@ -357,9 +361,10 @@ int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
               int* err) {
     RLB_TRY(load_encode());
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
-    // scratch: [x hi | x lo] for the f32 form, then up to 8 split-K slabs
+    // scratch: [x hi | x lo] for the f32 form, then the split-K slabs (if any)
     const size_t xs = TF32 ? (((size_t)n * K * sizeof(float) + 255) & ~(size_t)255) : 0;
-    RLB_TRY(reserve_scratch(ctx, 2 * xs + (size_t)8 * n * M * sizeof(float)));
+    const int splits = pick_splits(ctx, ((M + BM - 1) / BM) * ((n + bn - 1) / bn), (K + BK - 1) / BK * (TF32 ? 2 : 1));
+    RLB_TRY(reserve_scratch(ctx, 2 * xs + (splits > 1 ? (size_t)splits * n * M * sizeof(float) : 0)));
     CUtensorMap tw, tx, tx2;
     RLB_TRY(make_map(&tw, W, M, K, ldw, BM, TF32));
     if (TF32) {
