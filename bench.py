@@ -363,7 +363,7 @@ def main():
         achieved = alg / (ms_per_token * 1e-3) / 1e9 / world  # per GPU
         traffic = None
         tp = os.path.join(ROOT, "profiles", "decode_step_7b_f16_traffic.txt")
-        if os.path.exists(tp) and args.workload == "7b" and world == 1 and not args.layers:
+        if os.path.exists(tp) and args.workload == "7b" and cfg["f16"] and world == 1 and not args.layers:
             # dram__bytes_read.sum + dram__bytes_write.sum per decoded token, from the ncu capture
             # summarised beside that file
             for ln in open(tp):
