@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path: LLaMA-7B-shape f16, batch 1, greedy decode after a
-128-token prefill (BASELINE.json configs[1]); tensor-parallel over N GPUs for N > 1.
+128-token prompt prefill; tensor-parallel over N GPUs for N > 1.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 7b|13b|30b|65b|tiny] [--impl reference]
 
@@ -10,11 +10,16 @@ A "step" is one decoded token. Prints ONE JSON line (rank 0).
  * e2e          the same loop through Transformer.forward with HOST tokens in and HOST logits
                 out every step (pinned staging copies inside the timed region), arg-max on the host;
  * roofline     algorithmic bytes per decoded token / time per token against the measured HBM peak;
- * cpu_baseline the CPU oracle (a restatement of the reference's AVX2 path) timed on this box's
-                host cores on a bounded sample.
+ * cpu_baseline the CPU oracle (a restatement of the reference's AVX2 path) at the full depth of the
+                workload: the real prompt is prefilled, then decode steps are timed on this box's
+                host cores (mean without the first token, as src/rllama_main.rs:905-921 does); its
+                greedy tokens are compared with the GPU's on the same weights;
+ * config.also  (N >= 2, default workload) a second measurement on the 65B shape: 1792-token prompt,
+                decode at context ~1800.
 With --impl reference only the CPU oracle runs (the reference is Rust and cannot be built here).
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -33,6 +38,8 @@ from rllama_b200 import synthetic as S  # noqa: E402
 
 METRIC = "decode_tokens_per_s"
 UNIT = "tokens/s"
+NOMINAL_HBM_GBS = 8000.0   # the per-GPU figure the target fractions were first stated against
+CPU_TIMED_STEPS = 24       # decode steps the CPU oracle is timed on (three groups of eight)
 
 
 def algorithmic_bytes_per_token(cfg, t_mean, f16=True, head_bytes=4):
@@ -44,6 +51,12 @@ def algorithmic_bytes_per_token(cfg, t_mean, f16=True, head_bytes=4):
     kv = L * 2 * t_mean * d * bw + L * 2 * d * bw
     small = (2 * L + 1) * d * 4 + d * 4
     return weights + kv + small
+
+
+def prefill_flops(cfg, P):
+    """2 n (4 d^2 + 3 d F) per layer + causal attention + the last row's head."""
+    d, F, L, V = cfg["dim"], cfg["ffn"], cfg["n_layers"], cfg["vocab"]
+    return 2.0 * P * L * (4 * d * d + 3 * d * F) + 2.0 * L * P * (P + 1) * d + 2.0 * V * d
 
 
 def measured_peak_gbs():
@@ -122,61 +135,78 @@ def torch_weights(cfg, device, seed=1234):
         yield kind, layer, t.half()
 
 
-def time_oracle(cfg, n_layers_list, steps, prompt_len, threads):
-    """Times the CPU oracle's decode step at reduced depths; returns ms/token extrapolated
-    linearly in depth to cfg['n_layers'] and the description of the sample."""
+def workload_name(cfg):
+    return "llama-%s-shape %s batch-1: %d-token prompt prefill then greedy decode (dim %d, %d layers, %d heads, ffn %d, vocab %d)" % (
+        cfg["name"], "f16" if cfg["f16"] else "f32", cfg["prompt"], cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"])
+
+
+def workload_config(cfg, gpus):
+    """The keys that name the workload; both arms print exactly these."""
+    return {"workload": workload_name(cfg), "model": cfg["name"], "weights": "f16" if cfg["f16"] else "f32",
+            "prompt_tokens": cfg["prompt"], "depth": cfg["n_layers"], "gpus": gpus}
+
+
+# ---- CPU oracle legs --------------------------------------------------------------------------
+def new_oracle(cfg, max_seq, threads):
     from oracle import oracle as O
-    per_depth = {}
-    for nl in n_layers_list:
-        sub = dict(cfg); sub["n_layers"] = nl
-        m = O.OracleTransformer(sub["dim"], nl, sub["n_heads"], sub["ffn"], sub["vocab"], sub["norm_eps"], prompt_len + steps + 2,
-                                sub["f16"], nthreads=threads)
-        for kind, layer in S.tensor_list(sub):
-            m.set_tensor(kind, layer, S.synth_tensor(kind, layer, sub))
-        c = m.make_caches()
-        toks = S.synth_tokens(prompt_len, sub["vocab"])
-        tok = int(toks[0])
-        pos = 0
-        # fill the cache token by token is too slow for long prompts; a short prefill stands in
-        logits = m.forward(toks[: min(prompt_len, 8)], 0, c)
-        pos = min(prompt_len, 8)
-        tok = int(np.argmax(logits))
-        m.forward([tok], pos, c)  # first decode step is not timed (as in src/rllama_main.rs:905-921)
-        pos += 1
+    return O.OracleTransformer(cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"], cfg["norm_eps"], max_seq,
+                               cfg["f16"], nthreads=threads)
+
+
+def time_oracle_decode(orc, cfg, prompt, warm, timed):
+    """The reference's own protocol on the CPU oracle at full depth: prefill the whole prompt, then greedy
+    single-token steps; `warm` untimed steps, then `timed` steps in three equal groups. Returns (median of
+    the group means in ms/token, all tokens produced, description)."""
+    c = orc.make_caches()
+    t0 = time.perf_counter()
+    logits = orc.forward(prompt, 0, c)
+    prefill_s = time.perf_counter() - t0
+    pos = len(prompt)
+    toks = [int(np.argmax(logits))]
+    for _ in range(max(1, warm)):  # the first decode step is never timed (src/rllama_main.rs:905-921)
+        logits = orc.forward([toks[-1]], pos, c); pos += 1
+        toks.append(int(np.argmax(logits)))
+    ctx0 = pos
+    groups = []
+    per = max(1, timed // 3)
+    for _ in range(3):
         t0 = time.perf_counter()
-        for _ in range(steps):
-            logits = m.forward([tok], pos, c)
-            tok = int(np.argmax(logits))
-            pos += 1
-        per_depth[nl] = (time.perf_counter() - t0) * 1e3 / steps
-        del m, c
-    (a, ta), (b, tb) = sorted(per_depth.items())[0], sorted(per_depth.items())[-1]
-    slope = (tb - ta) / (b - a) if b != a else tb / b
-    full = ta + slope * (cfg["n_layers"] - a)
-    sample = "%s-shape %s decode step on the CPU oracle, %s of %d layers + f32 head, %d tokens each at context ~%d, " \
-             "extrapolated linearly in depth" % (cfg["name"], "f16" if cfg["f16"] else "f32", "/".join(str(k) for k in sorted(per_depth)),
-                                                  cfg["n_layers"], steps, pos)
-    return full, sample, per_depth
+        for _ in range(per):
+            logits = orc.forward([toks[-1]], pos, c); pos += 1
+            toks.append(int(np.argmax(logits)))
+        groups.append((time.perf_counter() - t0) * 1e3 / per)
+    ms = statistics.median(groups)
+    sample = ("%s-shape %s on the CPU oracle at full depth (%d layers + f32 head): %d-token prompt prefilled (%.1f s), %d untimed "
+              "then 3 x %d timed greedy decode steps at context %d-%d, median of the three group means (%.1f / %.1f / %.1f ms per token)"
+              % (cfg["name"], "f16" if cfg["f16"] else "f32", cfg["n_layers"], len(prompt), prefill_s, max(1, warm), per, ctx0, pos,
+                 groups[0], groups[1], groups[2]))
+    return ms, toks, sample, {"prefill_s": prefill_s, "context_start": ctx0, "context_end": pos, "group_ms": groups}
 
 
 def run_reference(args, cfg, rank):
+    """--impl reference: the CPU oracle port alone, weights generated on the host."""
     if rank != 0:
         return
+    import torch
     from oracle import oracle as O
     threads = O.hw_threads()
-    depths = [1, 3] if cfg["n_layers"] >= 3 else [cfg["n_layers"]]
-    ms_list = []
-    per = None
-    for _ in range(max(1, min(args.steps, 3))):
-        ms, sample, per = time_oracle(cfg, depths, 3, 16, threads)
-        ms_list.append(ms)
-    ms = statistics.median(ms_list)
+    P = cfg["prompt"]
+    timed = max(3, min(args.steps, CPU_TIMED_STEPS) // 3 * 3)
+    warm = max(1, min(args.warmup, 4))
+    orc = new_oracle(cfg, P + warm + timed + 2, threads)
+    for kind, layer, t in torch_weights(cfg, torch.device("cpu")):
+        orc.set_tensor(kind, layer, t.numpy())
+        del t
+    prompt = S.synth_tokens(P, cfg["vocab"])
+    ms, toks, sample, info = time_oracle_decode(orc, cfg, prompt, warm, timed)
     val = 1e3 / ms
+    config = workload_config(cfg, args.gpus)
+    config.update({"context_start": info["context_start"], "context_end": info["context_end"], "timed_steps": timed,
+                   "note": "the reference is Rust (no toolchain on this box): its CPU restatement is timed, on every host thread"})
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16" if cfg["f16"] else "f32", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), "note": "reference is Rust (no toolchain here): the CPU oracle port is timed instead"},
+        "dtype": "f16" if cfg["f16"] else "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -184,9 +214,136 @@ def run_reference(args, cfg, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_name(cfg):
-    return "llama-%s-shape %s batch-1: %d-token prompt prefill then greedy decode (dim %d, %d layers, %d heads, ffn %d, vocab %d)" % (
-        cfg["name"], "f16" if cfg["f16"] else "f32", cfg["prompt"], cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"])
+# ---- GPU legs ---------------------------------------------------------------------------------
+class Dist:
+    """The few collective helpers the bench needs; no-ops on one rank."""
+
+    def __init__(self, world, device):
+        self.world, self.device = world, device
+
+    def barrier(self, cl):
+        import torch
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+        cl.flush()
+
+    def max(self, v):
+        if self.world == 1:
+            return float(v)
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([v], device=self.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather(self, array):
+        """Every rank's copy of a numpy array (same shape on all ranks)."""
+        if self.world == 1:
+            return [array]
+        import torch
+        import torch.distributed as dist
+        t = torch.from_numpy(np.ascontiguousarray(array)).to(self.device)
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(out, t)
+        return [o.cpu().numpy() for o in out]
+
+
+def build_model(cfg, max_seq, cl, rank, world, device, oracle=None):
+    import torch
+    import torch.distributed as dist
+    from rllama_b200 import DataSettings, Transformer
+    ds = DataSettings(cl=cl)
+    if cfg["f16"]:
+        ds = ds.force_f16()
+    model = Transformer(cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"], max_seq, cfg["norm_eps"], ds,
+                        tp_rank=rank, tp_size=world)
+    for kind, layer, t in torch_weights(cfg, device):
+        model.set_tensor(kind, layer, t)
+        if oracle is not None:  # the same values go to the CPU oracle (the checker of the cpu_baseline leg)
+            oracle.set_tensor(kind, layer, t.cpu().numpy())
+        del t
+    model.finalize()
+    torch.cuda.empty_cache()
+    if world > 1:
+        ids = [Transformer.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        model.nccl_init(ids[0])
+        if os.environ.get("RLB_TP_MODE", "push") == "push":
+            handles = [None] * world
+            dist.all_gather_object(handles, model.peer_export())
+            model.peer_import(handles)
+            model.set_tp_mode("push")
+    return model
+
+
+def measure(model, cfg, cl, D, local_rank, K, Wm, do_e2e=True):
+    """Warm prefill, Wm untimed + K timed device-fed decode steps, then the host-buffer loop."""
+    P = cfg["prompt"]
+    prompt = S.synth_tokens(P, cfg["vocab"])
+    # the first prefill also pays for buffer allocation and module loading: time the second one
+    scratch = model.make_caches()
+    model.forward_greedy(prompt, 0, scratch)
+    scratch.free()
+    caches = model.make_caches()
+    D.barrier(cl)
+    t0 = time.perf_counter()
+    first = model.forward_greedy(prompt, 0, caches)
+    cl.flush()
+    prefill_ms = D.max((time.perf_counter() - t0) * 1e3)
+    warm_tokens, _ = model.decode_greedy(first, P, Wm, caches)
+    sampler = ClockSampler(local_rank)
+    D.barrier(cl)
+    launches0 = cl.kernel_launches()
+    sampler.start()
+    tokens, dev_ms = model.decode_greedy(int(warm_tokens[-1]), P + Wm, K, caches)
+    D.barrier(cl)
+    clocks = sampler.stop()
+    launches = cl.kernel_launches() - launches0
+    dev_ms = D.max(dev_ms)
+    caches.free()
+    all_tokens = np.concatenate([[first], warm_tokens, tokens]).astype(np.int32)
+    out = {"P": P, "prefill_ms": prefill_ms, "ms_per_token": dev_ms / K, "launches": int(launches), "clocks": clocks,
+           "tokens": all_tokens, "kernels_per_step": int(model.get_stat("kernels_per_step"))}
+
+    # every rank must have decoded the same tokens
+    gathered = D.gather(all_tokens)
+    out["ranks_agree_tokens"] = all(np.array_equal(gathered[0], g) for g in gathered)
+
+    if do_e2e:
+        # end-to-end loop through Transformer.forward with host buffers
+        c2 = model.make_caches()
+        logits = model.forward(prompt, 0, c2)
+        tok = int(np.argmax(logits))
+        pos = P
+        for _ in range(Wm):
+            logits = model.forward([tok], pos, c2); tok = int(np.argmax(logits)); pos += 1
+        D.barrier(cl)
+        t0 = time.perf_counter()
+        for _ in range(K):
+            logits = model.forward([tok], pos, c2)
+            tok = int(np.argmax(logits))
+            pos += 1
+        D.barrier(cl)
+        e2e_ms = D.max((time.perf_counter() - t0) * 1e3)
+        out["e2e"] = {"value": 1e3 * K / e2e_ms, "unit": UNIT, "ms_per_token": e2e_ms / K, "h2d_bytes_per_step": 8,
+                      "d2h_bytes_per_step": 4 * cfg["vocab"]}
+        c2.free()
+        # the last step's logits, rank against rank (every rank assembles the full vocabulary)
+        gl = D.gather(logits)
+        out["ranks_logit_max_abs_diff"] = float(max(np.abs(g - gl[0]).max() for g in gl))
+    return out
+
+
+def roofline_of(cfg, m, K, Wm, world):
+    t_mean = m["P"] + Wm + (K + 1) / 2.0
+    alg = algorithmic_bytes_per_token(cfg, t_mean, cfg["f16"])
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg / (m["ms_per_token"] * 1e-3) / 1e9 / world  # per GPU
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "peak_source": peak_kind, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "algorithmic_bytes_per_token": alg,
+            "launch": "one decode step (one CUDA-graph launch, %d kernels)" % m["kernels_per_step"]}
 
 
 def gemm_sweep():
@@ -221,8 +378,10 @@ def main():
     ap.add_argument("--workload", default="7b")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--layers", type=int, default=0, help="override depth (debugging; makes the number invalid as a headline)")
+    ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the second (65B-shape) measurement of multi-GPU runs")
     ap.add_argument("--profile-kernels", action="store_true", help="also time each kernel class with events (eager, untimed extra pass)")
     ap.add_argument("--f32", action="store_true", help="keep the weights and caches in f32 (the reference without --f16)")
     ap.add_argument("--gemm-sweep", action="store_true",
@@ -236,6 +395,8 @@ def main():
         cfg["f16"] = False
     if args.layers:
         cfg["n_layers"] = args.layers
+    if args.prompt:
+        cfg["prompt"] = args.prompt
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -249,96 +410,27 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from rllama_b200 import Cuda, DataSettings, Transformer
+    from rllama_b200 import Cuda
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    D = Dist(world, device)
 
-    P, K, Wm = cfg["prompt"], args.steps, args.warmup
-    max_seq = max(cfg["max_seq_len"], P + Wm + K + 1)
+    K, Wm = args.steps, args.warmup
     cl = Cuda(verbose=False, nth_device=local_rank)
-    ds = DataSettings(cl=cl)
-    if cfg["f16"]:
-        ds = ds.force_f16()
-    model = Transformer(cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"], max_seq, cfg["norm_eps"], ds,
-                        tp_rank=rank, tp_size=world)
-    for kind, layer, t in torch_weights(cfg, device):
-        model.set_tensor(kind, layer, t)
-        del t
-    model.finalize()
-    torch.cuda.empty_cache()
-    if world > 1:
-        ids = [Transformer.nccl_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(ids, src=0)
-        model.nccl_init(ids[0])
-        tp_mode = os.environ.get("RLB_TP_MODE", "push")
-        if tp_mode == "push":
-            handles = [None] * world
-            dist.all_gather_object(handles, model.peer_export())
-            model.peer_import(handles)
-            model.set_tp_mode("push")
-
-    prompt = S.synth_tokens(P, cfg["vocab"])
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        cl.flush()
-
-    # ---- device-resident loop ("value") ---------------------------------------------------
-    # the first prefill also pays for buffer allocation and module loading: time the second one
-    scratch_caches = model.make_caches()
-    model.forward_greedy(prompt, 0, scratch_caches)
-    scratch_caches.free()
-    caches = model.make_caches()
-    barrier()
-    t0 = time.perf_counter()
-    first = model.forward_greedy(prompt, 0, caches)
-    cl.flush()
-    prefill_ms = (time.perf_counter() - t0) * 1e3
-    warm_tokens, _ = model.decode_greedy(first, P, Wm, caches)
-    sampler = ClockSampler(local_rank)
-    barrier()
-    launches0 = cl.kernel_launches()
-    sampler.start()
-    tokens, dev_ms = model.decode_greedy(int(warm_tokens[-1]), P + Wm, K, caches)
-    barrier()
-    clocks = sampler.stop()
-    launches = cl.kernel_launches() - launches0
-    if world > 1:
-        t = torch.tensor([dev_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms = float(t.item())
-    ms_per_token = dev_ms / K
-    value = 1e3 / ms_per_token
-
-    # ---- end-to-end loop through Transformer.forward with host buffers ---------------------
-    e2e = None
-    if not args.no_e2e:
-        c2 = model.make_caches()
-        logits = model.forward(prompt, 0, c2)
-        tok = int(np.argmax(logits))
-        pos = P
-        for _ in range(Wm):
-            logits = model.forward([tok], pos, c2); tok = int(np.argmax(logits)); pos += 1
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(K):
-            logits = model.forward([tok], pos, c2)
-            tok = int(np.argmax(logits))
-            pos += 1
-        barrier()
-        e2e_ms = (time.perf_counter() - t0) * 1e3
-        if world > 1:
-            t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        e2e = {"value": 1e3 * K / e2e_ms, "unit": UNIT, "ms_per_token": e2e_ms / K, "h2d_bytes_per_step": 8,
-               "d2h_bytes_per_step": 4 * cfg["vocab"]}
-        c2.free()
+    want_cpu = world == 1 and not args.no_cpu_baseline
+    oracle = None
+    cpu_timed = max(3, min(K, CPU_TIMED_STEPS) // 3 * 3)
+    cpu_warm = max(1, min(Wm, 4))
+    if want_cpu:
+        from oracle import oracle as O
+        threads = O.hw_threads()
+        oracle = new_oracle(cfg, cfg["prompt"] + cpu_warm + cpu_timed + 2, threads)
+    max_seq = max(cfg["max_seq_len"], cfg["prompt"] + Wm + K + 1)
+    model = build_model(cfg, max_seq, cl, rank, world, device, oracle)
+    m = measure(model, cfg, cl, D, local_rank, K, Wm, do_e2e=not args.no_e2e)
 
     kernels = None
     if args.profile_kernels:
@@ -346,49 +438,73 @@ def main():
         # tensor parallelism a class's time includes waiting for the other ranks' partial sums.
         model.set_option("profile", 1)
         c3 = model.make_caches()
-        f3 = model.forward_greedy(prompt, 0, c3)
-        model.decode_greedy(f3, P, 16, c3)
+        f3 = model.forward_greedy(S.synth_tokens(cfg["prompt"], cfg["vocab"]), 0, c3)
+        model.decode_greedy(f3, cfg["prompt"], 16, c3)
         n = model.get_stat("prof_steps")
         kernels = {k: model.get_stat("prof_ms_" + k) / n for k in ("qkv", "attn", "wo", "w13", "w2", "head", "argmax", "comm")}
         model.set_option("profile", 0)
         c3.free()
+    model.free()
+    torch.cuda.empty_cache()
+
+    # ---- second measurement: the 65B shape under tensor parallelism ---------------------------
+    also = None
+    if world >= 2 and args.workload == "7b" and not args.no_also and not args.layers and not args.f32:
+        big = dict(S.CONFIGS["65b"]); big["name"] = "65b"
+        max_seq_b = max(big["max_seq_len"], big["prompt"] + Wm + K + 1)
+        model_b = build_model(big, max_seq_b, cl, rank, world, device)
+        mb = measure(model_b, big, cl, D, local_rank, K, Wm, do_e2e=False)
+        rb = roofline_of(big, mb, K, Wm, world)
+        also = {"workload": workload_name(big), "parallelism": "tp%d" % world, "ms_per_token": mb["ms_per_token"],
+                "tokens_per_s": 1e3 / mb["ms_per_token"], "context_start": mb["P"] + Wm, "context_end": mb["P"] + Wm + K,
+                "frac_of_measured_peak": rb["frac"], "frac_of_nominal_8TBs": rb["frac_of_nominal_8TBs"],
+                "algorithmic_bytes_per_token": rb["algorithmic_bytes_per_token"], "prefill_ms": mb["prefill_ms"],
+                "prefill_tflops_per_gpu": prefill_flops(big, mb["P"]) / (mb["prefill_ms"] * 1e-3) / 1e12 / world,
+                "tokens_sha1": hashlib.sha1(mb["tokens"].tobytes()).hexdigest(), "ranks_agree_tokens": mb["ranks_agree_tokens"],
+                "clocks": mb["clocks"]}
+        model_b.free()
 
     if rank == 0:
-        # prefill arithmetic: 2 n (4 d^2 + 3 d F) per layer + causal attention + the last row's head
-        d_, F_, L_, V_ = cfg["dim"], cfg["ffn"], cfg["n_layers"], cfg["vocab"]
-        prefill_flops = 2.0 * P * L_ * (4 * d_ * d_ + 3 * d_ * F_) + 2.0 * L_ * P * (P + 1) * d_ + 2.0 * V_ * d_
-        t_mean = P + Wm + (K + 1) / 2.0
-        alg = algorithmic_bytes_per_token(cfg, t_mean, cfg["f16"])
-        peak, peak_kind = measured_peak_gbs()
-        achieved = alg / (ms_per_token * 1e-3) / 1e9 / world  # per GPU
-        traffic = None
+        roof = roofline_of(cfg, m, K, Wm, world)
         tp = os.path.join(ROOT, "profiles", "decode_step_7b_f16_traffic.txt")
         if os.path.exists(tp) and args.workload == "7b" and cfg["f16"] and world == 1 and not args.layers:
             # dram__bytes_read.sum + dram__bytes_write.sum per decoded token, from the ncu capture
             # summarised beside that file
             for ln in open(tp):
                 if ln.startswith("dram_bytes_per_token"):
-                    traffic = int(ln.split("=")[1])
+                    roof["traffic"] = int(ln.split("=")[1])
+        config = workload_config(cfg, world)
+        config.update({
+            "parallelism": "tp%d" % world, "exchange": (os.environ.get("RLB_TP_MODE", "push") if world > 1 else "none"),
+            "context_start": m["P"] + Wm, "context_end": m["P"] + Wm + K,
+            "l2": "inputs larger than L2 (every step streams all weights)", "prefill_ms": m["prefill_ms"],
+            "prefill_tflops_per_gpu": prefill_flops(cfg, m["P"]) / (m["prefill_ms"] * 1e-3) / 1e12 / world,
+            # all decoded tokens (first after the prompt, warm-up, timed): same seed and warm-up at every N
+            "tokens_sha1": hashlib.sha1(m["tokens"].tobytes()).hexdigest(), "tokens_head": [int(t) for t in m["tokens"][:16]],
+            "ranks_agree": {"tokens": m["ranks_agree_tokens"], "last_logits_max_abs_diff": m.get("ranks_logit_max_abs_diff")},
+        })
+        if also:
+            config["also"] = also
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
-            "ms_per_step": ms_per_token, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16" if cfg["f16"] else "f32", "data": "synthetic",
-            "config": {"workload": workload_name(cfg), "parallelism": "tp%d" % world, "exchange": (os.environ.get("RLB_TP_MODE", "push") if world > 1 else "none"), "context_start": P + Wm, "context_end": P + Wm + K,
-                       "l2": "inputs larger than L2 (every step streams all weights)", "prefill_ms": prefill_ms,
-                       "prefill_tflops_per_gpu": prefill_flops / (prefill_ms * 1e-3) / 1e12 / world,
-                       "first_tokens": [int(first)] + [int(t) for t in tokens[:4]]},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes_per_token": alg,
-                         "launch": "one decode step (one CUDA-graph launch, %d kernels)" % int(model.get_stat("kernels_per_step"))},
-            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "metric": METRIC, "value": 1e3 / m["ms_per_token"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
+            "ms_per_step": m["ms_per_token"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16" if cfg["f16"] else "f32", "data": "synthetic", "config": config, "roofline": roof,
+            "e2e": m.get("e2e"), "gpu_launches": m["launches"], "clocks": m["clocks"],
         }
         if kernels:
             line["kernel_ms"] = kernels
-        if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle as O
-            threads = O.hw_threads()
-            ms, sample, _ = time_oracle(cfg, [1, 3] if cfg["n_layers"] >= 3 else [cfg["n_layers"]], 3, 16, threads)
+        if want_cpu:
+            prompt = S.synth_tokens(cfg["prompt"], cfg["vocab"])
+            ms, otoks, sample, _ = time_oracle_decode(oracle, cfg, prompt, cpu_warm, cpu_timed)
             line["cpu_baseline"] = {"value": 1e3 / ms, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+            # the oracle as checker: its greedy tokens against the GPU's on the same weights and prompt
+            n = min(len(otoks), len(m["tokens"]))
+            same = 0
+            while same < n and int(otoks[same]) == int(m["tokens"][same]):
+                same += 1
+            config["oracle_check"] = {"tokens_compared": n, "identical_prefix": same,
+                                      "note": "greedy tokens of the CPU oracle and the GPU path at full depth, same weights; a "
+                                              "difference is possible at a near-tie of two f16 logits and ends the comparison"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -299,8 +299,7 @@ int rlb_sampler_candidates(rlb_sampler* s, const float* logits, int32_t vocab, c
 
 /* Tuning and inspection. Options: "graph" (replay the decode step as a CUDA graph, default 1),
  * "stream_gemv" (bulk-copy staged GEMV kernels, default 1), "pdl" (programmatic dependent launch,
- * default 1), "persistent" (one cooperative kernel per token, default 0), "profile" (time every
- * kernel class of the decode step). Statistics: "kernels_per_step", "attn_split", "local_heads",
+ * default 1), "profile" (time every kernel class of the decode step). Statistics: "kernels_per_step", "attn_split", "local_heads",
  * "first_head", "local_ffn", "local_vocab", "vocab_size", "ffn_dim", "prof_steps", "prof_ms_<qkv|attn|wo|w13|w2|head|argmax|comm>". */
 int rlb_model_set_option(rlb_model* m, const char* name, int64_t value);
 int rlb_model_get_stat(rlb_model* m, const char* name, double* value);

@@ -154,14 +154,15 @@ struct Mat {
     }
     ~Mat() { release(); }
     void release() { if (data) free(data); data = nullptr; }
-    void alloc(int64_t r, int64_t c, bool f16) {
+    // zero = false: the caller overwrites every element (only allowed when rows carry no padding)
+    void alloc(int64_t r, int64_t c, bool f16, bool zero = true) {
         release();
         rows = r; cols = c; is_f16 = f16;
         cap = round_up(c, f16 ? 16 : 8);
         size_t bytes = (size_t)std::max<int64_t>(r, 1) * cap * (f16 ? 2 : 4);
         bytes = (size_t)round_up((int64_t)bytes, 32);
         data = aligned_alloc(32, bytes);
-        memset(data, 0, bytes);
+        if (zero || cap != c || r < 1) memset(data, 0, bytes);
     }
     float* f32() { return (float*)data; }
     const float* f32() const { return (const float*)data; }
@@ -504,13 +505,17 @@ void orc_model_free(void* mp) { delete (Model*)mp; }
 // embeddings, gains and the output head stay f32 (:302-308, :468).
 int orc_model_set_tensor(void* mp, int kind, int layer, const void* data, int rows, int cols, int dtype) {
     Model* m = (Model*)mp;
-    Mat src(rows, cols, dtype == 1);
+    Mat src;
+    src.alloc(rows, cols, dtype == 1, false);
     const size_t esz = dtype == 1 ? 2 : 4;
     for (int r = 0; r < rows; r++)
         memcpy((char*)src.data + (size_t)r * src.cap * esz, (const char*)data + (size_t)r * cols * esz, (size_t)cols * esz);
-    Mat f32m = cast(src, false);
+    // The reference widens every loaded tensor to f32 and, under --f16, narrows the seven per-layer matrices
+    // again (src/tensor.rs:2388-2545, src/transformer.rs:514-525). f16 -> f32 -> f16 is the identity, so a
+    // tensor that arrives in the type it is stored in is kept as it is.
     bool per_layer_matrix = kind >= K_WQ && kind <= K_W3;
-    Mat stored = (per_layer_matrix && m->force_f16) ? cast(f32m, true) : std::move(f32m);
+    const bool want_f16 = per_layer_matrix && m->force_f16;
+    Mat stored = (src.is_f16 == want_f16) ? std::move(src) : cast(src, want_f16);
     if (kind != K_TOK_EMB && kind != K_NORM && kind != K_OUTPUT && (layer < 0 || layer >= m->n_layers)) return -1;
     switch (kind) {
         case K_TOK_EMB: m->tok_emb = std::move(stored); break;

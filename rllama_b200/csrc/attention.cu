@@ -13,6 +13,7 @@
 // head, so that one position's vector is a single coalesced read.
 #include "internal.h"
 
+#include <atomic>
 #include <cfloat>
 #include <cstdlib>
 #include <cstdio>
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_kernel(const AttnDecodeA
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int hd = a.hd, head = blockIdx.x, split = blockIdx.y, ns = a.n_split;
-    const int T = *a.pos_ptr + 1;
+    const int T = (a.pos_ptr ? *a.pos_ptr : a.pos_value) + 1;
     int chunk = (T + ns - 1) / ns;
     chunk = (chunk + 31) & ~31;
     const int t0 = min(T, split * chunk), t1 = min(T, t0 + chunk);
@@ -431,12 +432,15 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     __shared__ float w_o[kWarps][HD];
     __shared__ unsigned int ticket_sh;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A CTA's shared memory may be written by its cluster peers only once that CTA is running: every CTA
+    // announces itself here and waits for all of them just before its first remote store.
+    if constexpr (CL) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     // Before waiting for the projection kernel: the position (only the last kernel of a decode step
     // changes it) and the cache rows of earlier positions (written by earlier steps) are already
     // final, so the first batch of K and V rows is requested now and its latency overlaps the wait.
     const int head = blockIdx.x, split = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int T = *a.pos_ptr + 1;
+    const int T = (a.pos_ptr ? *a.pos_ptr : a.pos_value) + 1;
     const int chunk = fast_chunk(T, a.n_split);
     const int active = (T + chunk - 1) / chunk;  // splits with at least one position
     const bool work = split < active;
@@ -528,6 +532,7 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
     if constexpr (CL) {
         __shared__ float r_o[8][HD];
         __shared__ float r_m[8], r_l[8];
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster has started
         if (work) {
             if (c < HD) cluster_store(cluster_map(&r_o[split][c], 0), o);
             if (c == 0) {
@@ -646,12 +651,12 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
         void* kargs[] = {(void*)&a};
         RLB_CUDA(cudaLaunchKernelExC(&lc, kern, kargs));
     } else if (cache_dtype == RLB_F16) {
-        static bool set = false;
-        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        static std::atomic<uint64_t> set{0};
+        if (!attr_done(set, ctx->device)) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_mark(set, ctx->device); }
         RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_kernel<__half>, a));
     } else {
-        static bool set = false;
-        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        static std::atomic<uint64_t> set{0};
+        if (!attr_done(set, ctx->device)) { RLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_mark(set, ctx->device); }
         RLB_CUDA(cudaLaunchKernelEx(&lc, attn_decode_kernel<float>, a));
     }
     count_launch(ctx);
@@ -679,12 +684,12 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
     if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "attention: %d positions do not fit in shared memory", a.start_pos + a.n);
     dim3 grid(a.heads, a.n);
     if (cache_dtype == RLB_F16) {
-        static bool set = false;
-        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        static std::atomic<uint64_t> set{0};
+        if (!attr_done(set, ctx->device)) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_mark(set, ctx->device); }
         attn_prefill_kernel<__half><<<grid, kThreads, smem, ctx->stream>>>(a);
     } else {
-        static bool set = false;
-        if (!set) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        static std::atomic<uint64_t> set{0};
+        if (!attr_done(set, ctx->device)) { RLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); attr_mark(set, ctx->device); }
         attn_prefill_kernel<float><<<grid, kThreads, smem, ctx->stream>>>(a);
     }
     RLB_LAUNCH_CHECK();
@@ -700,8 +705,8 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
 // generated: an inference server that has already divided all of HBM between weights and KV
 // caches has nothing left for cudaMalloc to hand out, and a worker thread on the token path
 // cannot afford cudaMalloc / cudaFree, which stall every stream of the device while they run.
-// For those callers the split-attention kernel's scratch (per-split partial outputs, the
-// per-head arrival counters and the position word) lives in the fixed array below instead of
+// For those callers the split-attention kernel's scratch (per-split partial outputs and the
+// per-head arrival counters) lives in the fixed array below instead of
 // in memory obtained at call time. Every GPU that loads the library holds the array
 // (kStaticBytes) until the process exits.
 //
@@ -717,7 +722,7 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
 namespace {
 
 constexpr int kStaticMaxHeads = 256;
-constexpr size_t kStaticHeaderFloats = 64 + kStaticMaxHeads;      // position word (padded) + counters
+constexpr size_t kStaticHeaderFloats = 64 + kStaticMaxHeads;      // one unused 256-byte line + counters
 constexpr size_t kStaticRecordFloats = 256 * 1024;                // 1 MiB of partial records
 constexpr size_t kStaticFloats = kStaticHeaderFloats + kStaticRecordFloats;
 constexpr size_t kStaticBytes = kStaticFloats * sizeof(float);
@@ -760,12 +765,12 @@ extern "C" int rlb_attention_decode_static(rlb_tensor* out, const rlb_tensor* q,
     RLB_CUDA(cudaSetDevice(ctx->device));
     float* base = nullptr;
     RLB_TRY(static_scratch_address(ctx->device, &base));
-    // the position word and the arrival counters must start from known values on every call
+    // the arrival counters must start from zero on every call (an earlier call that was cut short may
+    // have left some behind); the position travels by value in the kernel's arguments
     RLB_CUDA(cudaMemsetAsync(base, 0, kStaticHeaderFloats * sizeof(float), ctx->stream));
-    RLB_CUDA(cudaMemcpyAsync(base, &pos, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
     AttnDecodeArgs a;
     a.q = (const float*)q->d; a.kcache = kcache->d; a.vcache = vcache->d; a.out = out->d;
-    a.pos_ptr = reinterpret_cast<const int32_t*>(base);
+    a.pos_ptr = nullptr; a.pos_value = pos;
     a.heads = heads; a.hd = hd; a.max_seq = max_seq_len; a.n_split = n_split;
     a.counters = reinterpret_cast<unsigned int*>(base + 64);
     a.scratch = base + kStaticHeaderFloats;

@@ -339,10 +339,10 @@ extern "C" int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const 
     }
     char* base = (char*)ctx->op_scratch;
     RLB_CUDA(cudaMemsetAsync(base, 0, 256 + cnt_bytes, ctx->stream));
-    RLB_CUDA(cudaMemcpyAsync(base, &pos, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
     AttnDecodeArgs a;
     a.q = (const float*)q->d; a.kcache = kcache->d; a.vcache = vcache->d; a.out = out->d;
-    a.pos_ptr = (const int32_t*)base; a.heads = heads; a.hd = hd; a.max_seq = max_seq_len; a.n_split = n_split;
+    a.pos_ptr = nullptr; a.pos_value = pos;  // by value: no copy from a stack variable on the stream
+    a.heads = heads; a.hd = hd; a.max_seq = max_seq_len; a.n_split = n_split;
     a.counters = (unsigned int*)(base + 256);
     a.scratch = (float*)(base + 256 + cnt_bytes);
     RLB_TRY(launch_attn_decode(ctx, kcache->dtype, a, 0));

@@ -299,10 +299,10 @@ int launch_argmax(rlb_ctx* ctx, const float* logits, int n, int32_t* out_tok, co
 
 int launch_argmax_advance(rlb_ctx* ctx, const float* logits, int n, int32_t* tok, int32_t* pos, int32_t* step, int32_t* tokens_out,
                           int32_t tokens_cap, const StepSync& sync) {
-    static bool carve_set = false;  // keep the shared-memory split of the projection kernels around it
-    if (!carve_set) {
+    static std::atomic<uint64_t> carve_set{0};  // keep the shared-memory split of the projection kernels around it
+    if (!attr_done(carve_set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        carve_set = true;
+        attr_mark(carve_set, ctx->device);
     }
     argmax_advance_kernel<<<1, 1024, 0, ctx->stream>>>(logits, n, tok, pos, step, tokens_out, tokens_cap, sync);
     RLB_LAUNCH_CHECK();

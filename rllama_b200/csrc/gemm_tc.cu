@@ -296,10 +296,10 @@ int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const 
     const int splits = pick_splits(ctx, (int)(grid.x * grid.y), (K + BK - 1) / BK * (TF32 ? 2 : 1));
     if (splits == 1) {
         auto kern = gemm_tc_kernel<BN, OT, TF32>;
-        static bool set = false;
-        if (!set) {
+        static std::atomic<uint64_t> set{0};
+        if (!attr_done(set, ctx->device)) {
             RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set = true;
+            attr_mark(set, ctx->device);
         }
         kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, C, ldc, n, M, K, round_out, 0, err);
         RLB_LAUNCH_CHECK();
@@ -311,10 +311,10 @@ int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const 
     if (need > ctx->gemm_scratch_bytes) return rlb_fail(RLB_ERR_STATE, "gemm: scratch of %zu bytes was not reserved", need);
     float* part = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + scratch_off);
     auto kern = gemm_tc_kernel<BN, float, TF32>;
-    static bool set = false;
-    if (!set) {
+    static std::atomic<uint64_t> set{0};
+    if (!attr_done(set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        set = true;
+        attr_mark(set, ctx->device);
     }
     grid.z = splits;
     kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, part, (int64_t)M, n, M, K, 0, (int64_t)n * M, err);

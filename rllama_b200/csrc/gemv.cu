@@ -259,14 +259,14 @@ void load_tuning() {
 
 template <typename WT, int R, int PRO, int EPI>
 int launch_one(rlb_ctx* ctx, const GemvArgs& a, int ctas_per_sm) {
-    static bool attr_set = false;
+    static std::atomic<uint64_t> attr_set{0};
     auto kern = gemv_kernel<WT, R, PRO, EPI>;
     size_t smem = (((size_t)a.K * sizeof(WT)) + 15) & ~(size_t)15;
     if (PRO == PRO_NORM) smem += (size_t)a.K * sizeof(float);
     if (smem > 200 * 1024) return rlb_fail(RLB_ERR_LIMIT, "gemv: activation row of %d elements does not fit in shared memory", a.K);
-    if (!attr_set) {
+    if (!attr_done(attr_set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_set = true;
+        attr_mark(attr_set, ctx->device);
     }
     const int n_groups = a.rows / R;
     int grid = (n_groups + kWarps - 1) / kWarps;

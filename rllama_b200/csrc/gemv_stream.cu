@@ -544,13 +544,13 @@ int launch_cfg(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     int stages = (int)((budget - fixed) / STAGE_BYTES);
     if (stages > g_st.max_stages) stages = g_st.max_stages;
     const size_t smem = fixed + (size_t)stages * STAGE_BYTES;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static std::atomic<uint64_t> attr_set{0};
+    if (!attr_done(attr_set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         // every kernel of the decode chain asks for the same shared-memory split, so that CTAs of
         // consecutive kernels can share an SM
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        attr_set = true;
+        attr_mark(attr_set, ctx->device);
     }
     const int n_tiles = a.rows / RB;
     const int max_grid = ctx->sm_count;

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <mutex>
@@ -136,66 +137,6 @@ int gemv_stream_grid(rlb_ctx* ctx, rlb_dtype dtype, int prologue, int epilogue, 
 void gemv_set_tuning(int rows_per_warp, int ctas_per_sm, int threads);
 
 // ---------------------------------------------------------------------------------------
-// persistent decode step (decode_mega.cu): one cooperative kernel walks a table of phases
-// ---------------------------------------------------------------------------------------
-enum MegaKind { MK_QKV = 0, MK_ATTN = 1, MK_PROJ = 2, MK_W13 = 3, MK_HEAD = 4, MK_ARGMAX = 5 };
-
-struct MegaPhase {
-    int kind = 0;
-    int rows = 0;         // output rows of the GEMV (w1/w3: rows of each of the two matrices)
-    int K = 0;
-    int wait_phase = -1;  // phase every CTA must have completed before this one starts, or -1
-    int in_seq = 0;       // 1-based index of the exchange whose partial sums the prologue consumes (0: none)
-    int out_seq = 0;      // 1-based index of the exchange the epilogue produces (0: none)
-    int use_tok = 0;      // first layer: the residual row is the embedding of scalars[0]
-    int x_which = 0;      // which published-residual buffer the prologue uses
-    const void* W = nullptr;
-    const void* W2 = nullptr;
-    const float* gain = nullptr;
-    const float* x_in = nullptr;
-    float* x_out = nullptr;
-    const void* vec_in = nullptr;  // wo / w2: activation row in the weight dtype
-    void* out = nullptr;           // w1/w3: gated activation
-    void* kcache = nullptr;
-    void* vcache = nullptr;
-    size_t inbox_off = 0;          // byte offsets inside the exchange buffer
-    size_t outbox_off = 0;
-    int64_t out_offset = 0;        // first entry this rank produces (rank * dim, or first vocabulary row)
-};
-
-struct MegaParams {
-    const MegaPhase* phases = nullptr;
-    int n_phases = 0;
-    int f16 = 0;
-    int dim = 0, nq = 0, hd = 0, heads = 0, max_seq = 0, vocab = 0;
-    float eps = 0.f;
-    int tp = 1, rank = 0;
-    const float* rope = nullptr;
-    float* qbuf = nullptr;
-    void* obuf = nullptr;
-    int32_t* scalars = nullptr;  // [0] token [1] position [2] step [3] arg-max [4] exchange epoch [5] launches [8] error word
-    int32_t* tokens_out = nullptr;
-    int tokens_cap = 0;
-    int advance = 0;
-    unsigned int* done = nullptr;  // [n_phases] completion counters, monotonic over launches
-    unsigned int* xready = nullptr;  // [n_phases] "new residual row published" counters, same convention
-    int* err = nullptr;
-    float* attn_scratch = nullptr;
-    unsigned int* attn_counters = nullptr;
-    int n_split = 1;
-    char* xbuf = nullptr;
-    char* peer_xbuf[RLB_MAX_TP] = {nullptr};
-    size_t x_off[2] = {0, 0};
-    size_t logits_off = 0;
-    float* logits = nullptr;
-    uint32_t seq_stride = 0;
-    int n_stages = 0, act_bytes = 0, tmp_bytes = 0;
-    unsigned long long* trace = nullptr;  // optional [n_phases + 1] nanosecond time stamps taken by CTA 0 at every phase start
-};
-int mega_pick_stages(size_t act_bytes, size_t tmp_bytes);
-int launch_decode_mega(rlb_ctx* ctx, const MegaParams& P);
-
-// ---------------------------------------------------------------------------------------
 // attention (attention.cu)
 // ---------------------------------------------------------------------------------------
 struct AttnDecodeArgs {
@@ -203,7 +144,8 @@ struct AttnDecodeArgs {
     const void* kcache = nullptr;  // [heads][max_seq][hd]
     const void* vcache = nullptr;
     void* out = nullptr;           // [heads*hd] in the weight dtype (rounded when f16)
-    const int32_t* pos_ptr = nullptr;  // attends to positions 0..*pos_ptr
+    const int32_t* pos_ptr = nullptr;  // attends to positions 0..*pos_ptr ...
+    int pos_value = 0;                 // ... or, when pos_ptr is null, to 0..pos_value
     int heads = 0, hd = 0, max_seq = 0;
     int n_split = 1;
     float* scratch = nullptr;      // [heads][n_split][hd + 2] partial (o, m, l)
@@ -289,6 +231,11 @@ int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* 
 // helpers
 // ---------------------------------------------------------------------------------------
 static inline void count_launch(rlb_ctx* ctx, uint64_t n = 1) { ctx->launches += n; }
+// Function attributes (shared-memory opt-in) are per device: a call site keeps one bit per device index in
+// `mask`, tests it with attr_done and sets it with attr_mark once cudaFuncSetAttribute has succeeded there.
+// Two threads may both set the attribute the first time; that is harmless.
+static inline bool attr_done(const std::atomic<uint64_t>& mask, int device) { return (mask.load(std::memory_order_acquire) >> (device & 63)) & 1u; }
+static inline void attr_mark(std::atomic<uint64_t>& mask, int device) { mask.fetch_or(1ull << (device & 63), std::memory_order_release); }
 #define RLB_LAUNCH_CHECK()                                                                         \
     do {                                                                                           \
         cudaError_t _e = cudaGetLastError();                                                       \

@@ -256,7 +256,7 @@ int zip_list(const std::string& path, std::vector<std::pair<std::string, ZipEntr
         if (!read_at(f, z64, rec, sizeof rec) || rd32(rec) != 0x06064b50u) return rlb_fail(RLB_ERR_INVALID, "%s: bad zip64 end record", path.c_str());
         n_entries = rd64(rec + 32); cd_size = rd64(rec + 40); cd_off = rd64(rec + 48);
     }
-    if (cd_off + cd_size > fsize) return rlb_fail(RLB_ERR_INVALID, "%s: central directory outside the file", path.c_str());
+    if (cd_size > fsize || cd_off > fsize - cd_size) return rlb_fail(RLB_ERR_INVALID, "%s: central directory outside the file", path.c_str());
     std::vector<unsigned char> cd((size_t)cd_size);
     if (!read_at(f, cd_off, cd.data(), (size_t)cd_size)) return rlb_fail(RLB_ERR_INVALID, "%s: cannot read the central directory", path.c_str());
     size_t p = 0;
@@ -271,13 +271,16 @@ int zip_list(const std::string& path, std::vector<std::pair<std::string, ZipEntr
         if (p + 46 + nlen + xlen + clen > cd.size()) return rlb_fail(RLB_ERR_INVALID, "%s: truncated central directory", path.c_str());
         const std::string name((const char*)&cd[p + 46], nlen);
         // zip64 extended information: the fields that overflowed, in this order
-        for (size_t x = p + 46 + nlen; x + 4 <= p + 46 + nlen + xlen;) {
+        const size_t x_end = p + 46 + nlen + xlen;  // end of this entry's extra field (inside cd, checked above)
+        for (size_t x = p + 46 + nlen; x + 4 <= x_end;) {
             const uint16_t id = rd16(&cd[x]), len = rd16(&cd[x + 2]);
+            const size_t f_end = x + 4 + (size_t)len;
+            if (f_end > x_end) return rlb_fail(RLB_ERR_INVALID, "%s: extra field of %s runs past its entry", path.c_str(), name.c_str());
             if (id == 0x0001) {
                 size_t q = x + 4;
-                if (ze.size == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { ze.size = rd64(&cd[q]); q += 8; }
-                if (ze.comp_size == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { ze.comp_size = rd64(&cd[q]); q += 8; }
-                if (local == 0xFFFFFFFFu && q + 8 <= x + 4 + len) { local = rd64(&cd[q]); q += 8; }
+                if (ze.size == 0xFFFFFFFFu && q + 8 <= f_end) { ze.size = rd64(&cd[q]); q += 8; }
+                if (ze.comp_size == 0xFFFFFFFFu && q + 8 <= f_end) { ze.comp_size = rd64(&cd[q]); q += 8; }
+                if (local == 0xFFFFFFFFu && q + 8 <= f_end) { local = rd64(&cd[q]); q += 8; }
             }
             x += 4 + (size_t)len;
         }

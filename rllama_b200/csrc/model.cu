@@ -109,10 +109,6 @@ struct rlb_model {
     // options / statistics
     bool w_f16_exact = true;  // every projection matrix arrived as f16 (or was checked): its f32 copy is exact in TF32
     bool use_graph = true;
-    bool use_mega = false;   // one persistent kernel per decoded token (decode_mega.cu); off by default: the
-                             // chain of dependent-launch kernels is faster (3.8 against 2.6 ms per 7B token when both were measured)
-    unsigned int* mega_done = nullptr;  // per-phase completion counters of the persistent kernel
-    unsigned long long* mega_trace = nullptr;  // per-phase time stamps (profiling)
     bool use_stream = true;  // bulk-copy staged GEMV kernels (gemv_stream.cu)
     bool use_pdl = true;     // programmatic dependent launch between the decode kernels
     bool profile = false;
@@ -131,8 +127,6 @@ struct rlb_caches {
     cudaGraphExec_t graph = nullptr;      // decode step that leaves the arg-max in scalars[3]
     cudaGraphExec_t graph_adv = nullptr;  // decode step with on-device token feedback
     uint64_t graph_gen = 0;               // model->graph_gen the graphs were captured under
-    MegaPhase* mega_phases = nullptr;     // device copy of the persistent kernel's phase table for these caches
-    int mega_n = 0;
     bool warmed = false;
 };
 
@@ -334,115 +328,10 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
     return RLB_OK;
 }
 
-// ---- persistent decode step ----------------------------------------------------------------
-// The persistent kernel takes the model when every GEMV splits into 8-row (w1/w3: 4-row) tiles,
-// the head dimension is 64 or 128 and, under tensor parallelism, the peer exchange is active.
-bool mega_supported(const rlb_model* m) {
-    if (!m->use_mega || !m->use_stream) return false;
-    if (m->tp > 1 && !push_mode(m)) return false;
-    if (m->hd != 64 && m->hd != 128) return false;
-    if (m->nq % 8 != 0 || m->p.dim % 8 != 0 || m->F % 8 != 0 || m->V % 8 != 0) return false;
-    const size_t wsz = m->wsz;
-    size_t act = std::max({(size_t)m->p.dim * wsz, (size_t)m->nq * wsz, (size_t)m->F * wsz, (size_t)m->p.dim * 4});
-    act = (act + 15) & ~(size_t)15;
-    const size_t tmp = std::max((size_t)m->p.dim * 4, (size_t)(2 * 8 + 8 * m->hd + 8) * 4);
-    return mega_pick_stages(act, tmp) >= 2;
-}
-
-int mega_prepare(rlb_model* m, rlb_caches* c) {
-    rlb_ctx* ctx = m->ctx;
-    const int L = m->p.n_layers, d = m->p.dim;
-    if (!m->xbuf) {  // single GPU: the exchange entries live in local memory
-        if (m->tp > 1) return rlb_fail(RLB_ERR_STATE, "persistent decode: peer exchange buffers are not set up");
-        m->xbuf_bytes = xb_total(m);
-        RLB_TRY(dev_alloc((void**)&m->xbuf, m->xbuf_bytes));
-        RLB_CUDA(cudaMemsetAsync(m->xbuf, 0, m->xbuf_bytes, ctx->stream));
-        m->peer_xbuf[0] = m->xbuf;
-    }
-    const int n_phases = 5 * L + 2;
-    if (!m->mega_done) {  // [0, n) completion counters, [n, 2n) residual-published counters
-        RLB_TRY(dev_alloc_t(&m->mega_done, (size_t)2 * n_phases));
-        RLB_CUDA(cudaMemsetAsync(m->mega_done, 0, (size_t)2 * n_phases * sizeof(unsigned int), ctx->stream));
-    }
-    if (c->mega_phases) return RLB_OK;
-    std::vector<MegaPhase> ph((size_t)n_phases);
-    for (int l = 0; l < L; l++) {
-        const LayerW& W = m->L[l];
-        void* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
-        void* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
-        MegaPhase& q = ph[5 * l + 0];
-        q.kind = MK_QKV; q.rows = 3 * m->nq; q.K = d; q.W = W.wqkv; q.gain = W.attn_norm;
-        if (l == 0) { q.x_in = m->tok_emb; q.use_tok = 1; }
-        else { q.x_in = m->xb; q.in_seq = 2 * (l - 1) + 2; q.inbox_off = xb_inbox_w2(m); }
-        q.x_out = m->xa; q.x_which = 0; q.kcache = kc; q.vcache = vc;
-        MegaPhase& a = ph[5 * l + 1];
-        a.kind = MK_ATTN; a.wait_phase = 5 * l + 0; a.kcache = kc; a.vcache = vc;
-        MegaPhase& o = ph[5 * l + 2];
-        o.kind = MK_PROJ; o.rows = d; o.K = m->nq; o.W = W.wo; o.vec_in = m->obuf; o.wait_phase = 5 * l + 1;
-        o.out_seq = 2 * l + 1; o.outbox_off = xb_inbox_wo(m); o.out_offset = (int64_t)m->rank * d;
-        MegaPhase& g = ph[5 * l + 3];
-        g.kind = MK_W13; g.rows = m->F; g.K = d; g.W = W.w1; g.W2 = W.w3; g.gain = W.ffn_norm;
-        g.x_in = m->xa; g.x_out = m->xb; g.x_which = 1; g.in_seq = 2 * l + 1; g.inbox_off = xb_inbox_wo(m); g.out = m->gbuf;
-        MegaPhase& w = ph[5 * l + 4];
-        w.kind = MK_PROJ; w.rows = d; w.K = m->F; w.W = W.w2; w.vec_in = m->gbuf; w.wait_phase = 5 * l + 3;
-        w.out_seq = 2 * l + 2; w.outbox_off = xb_inbox_w2(m); w.out_offset = (int64_t)m->rank * d;
-    }
-    MegaPhase& h = ph[5 * L];
-    h.kind = MK_HEAD; h.rows = m->V; h.K = d; h.W = m->output; h.gain = m->norm;
-    h.x_in = m->xb; h.x_out = m->xa; h.x_which = 0; h.in_seq = 2 * (L - 1) + 2; h.inbox_off = xb_inbox_w2(m);
-    h.out_seq = 2 * L + 1; h.outbox_off = xb_logits(m); h.out_offset = m->v0;
-    ph[5 * L + 1].kind = MK_ARGMAX;
-    RLB_TRY(dev_alloc_t(&c->mega_phases, (size_t)n_phases));
-    RLB_CUDA(cudaMemcpyAsync(c->mega_phases, ph.data(), (size_t)n_phases * sizeof(MegaPhase), cudaMemcpyHostToDevice, ctx->stream));
-    RLB_CUDA(cudaStreamSynchronize(ctx->stream));  // ph goes out of scope
-    c->mega_n = n_phases;
-    return RLB_OK;
-}
-
-int run_decode_mega(rlb_model* m, rlb_caches* c, bool advance) {
-    RLB_TRY(mega_prepare(m, c));
-    MegaParams P;
-    P.phases = c->mega_phases; P.n_phases = c->mega_n; P.f16 = m->wdt == RLB_F16;
-    P.dim = m->p.dim; P.nq = m->nq; P.hd = m->hd; P.heads = m->nh; P.max_seq = m->p.max_seq_len; P.vocab = m->p.vocab_size;
-    P.eps = m->p.norm_eps; P.tp = m->tp; P.rank = m->rank; P.rope = m->rope; P.qbuf = m->qbuf; P.obuf = m->obuf;
-    P.scalars = m->scalars; P.tokens_out = m->tokens_out; P.tokens_cap = m->tokens_cap; P.advance = advance ? 1 : 0;
-    P.done = m->mega_done; P.xready = m->mega_done + c->mega_n; P.err = m->scalars + 8;
-    P.attn_scratch = m->attn_scratch; P.attn_counters = m->attn_counters; P.n_split = m->n_split;
-    P.xbuf = m->xbuf;
-    for (int r = 0; r < m->tp; r++) P.peer_xbuf[r] = m->peer_xbuf[r];
-    P.x_off[0] = xb_x(m, 0); P.x_off[1] = xb_x(m, 1); P.logits_off = xb_logits(m); P.logits = m->logits;
-    P.seq_stride = 2u * (uint32_t)m->p.n_layers + 1u;
-    size_t act = std::max({(size_t)m->p.dim * m->wsz, (size_t)m->nq * m->wsz, (size_t)m->F * m->wsz, (size_t)m->p.dim * 4});
-    P.act_bytes = (int)((act + 15) & ~(size_t)15);
-    P.tmp_bytes = (int)std::max((size_t)m->p.dim * 4, (size_t)(2 * 8 + 8 * m->hd + 8) * 4);
-    P.n_stages = mega_pick_stages(P.act_bytes, P.tmp_bytes);
-    if (m->profile) {
-        if (!m->mega_trace) RLB_TRY(dev_alloc_t(&m->mega_trace, (size_t)c->mega_n + 1));
-        P.trace = m->mega_trace;
-    }
-    RLB_TRY(launch_decode_mega(m->ctx, P));
-    m->kernels_per_step = 1;
-    c->warmed = true;
-    if (m->profile) {  // per-phase times as seen by CTA 0 (waiting for other CTAs and ranks included)
-        std::vector<unsigned long long> t((size_t)c->mega_n + 1);
-        RLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
-        RLB_CUDA(cudaMemcpy(t.data(), m->mega_trace, t.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        const int L = m->p.n_layers;
-        static const int cls_of[5] = {PC_QKV, PC_ATTN, PC_WO, PC_W13, PC_W2};
-        for (int pi = 0; pi < c->mega_n; pi++) {
-            const int cls = pi < 5 * L ? cls_of[pi % 5] : (pi == 5 * L ? PC_HEAD : PC_ARGMAX);
-            m->prof_ms[cls] += (double)(t[pi + 1] - t[pi]) * 1e-6;
-        }
-        m->prof_steps++;
-    }
-    return RLB_OK;
-}
-
 // Runs one decode step: eagerly the first time on a cache object (which also loads every
 // kernel before any capture), then as a replayed CUDA graph.
 int run_decode_step(rlb_model* m, rlb_caches* c, bool advance, cudaGraphExec_t* slot) {
     rlb_ctx* ctx = m->ctx;
-    if (mega_supported(m)) return run_decode_mega(m, c, advance);
     if (!m->use_graph || m->profile || !c->warmed) {
         const uint64_t before = ctx->launches;
         RLB_TRY(enqueue_decode_step(m, c, advance));
@@ -668,7 +557,6 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
         return s;
     }
     if (const char* e = getenv("RLB_STREAM")) m->use_stream = atoi(e) != 0;
-    if (const char* e = getenv("RLB_MEGA")) m->use_mega = atoi(e) != 0;
     if (const char* e = getenv("RLB_PDL")) m->use_pdl = atoi(e) != 0;
     if (const char* e = getenv("RLB_GRAPH")) m->use_graph = atoi(e) != 0;
     if (ctx->verbose)
@@ -774,8 +662,6 @@ int rlb_model_free(rlb_model* m) {
     for (int r = 0; r < m->tp; r++)
         if (m->peers_open && r != m->rank && m->peer_xbuf[r]) cudaIpcCloseMemHandle(m->peer_xbuf[r]);
     if (m->xbuf) cudaFree(m->xbuf);
-    if (m->mega_done) cudaFree(m->mega_done);
-    if (m->mega_trace) cudaFree(m->mega_trace);
     void* ptrs[] = {m->tok_emb, m->norm, m->output, m->rope, m->xa, m->xb, m->qbuf, m->obuf, m->gbuf, m->part_wo, m->part_w2,
                     m->logits_local, m->logits, m->scalars, m->tokens_out, m->attn_scratch, m->attn_counters, m->pf_tokens, m->pf_x,
                     m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g3, m->pf_g, m->pf_last};
@@ -910,7 +796,6 @@ int rlb_caches_free(rlb_caches* c) {
     cudaStreamSynchronize(ctx->stream);
     if (c->graph) cudaGraphExecDestroy(c->graph);
     if (c->graph_adv) cudaGraphExecDestroy(c->graph_adv);
-    if (c->mega_phases) cudaFree(c->mega_phases);
     if (c->k) cudaFree(c->k);
     if (c->v) cudaFree(c->v);
     delete c;
@@ -1011,7 +896,6 @@ int rlb_model_set_option(rlb_model* m, const char* name, int64_t value) {
     std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
     if (!strcmp(name, "graph")) { m->use_graph = value != 0; return RLB_OK; }
     if (!strcmp(name, "stream_gemv")) { m->use_stream = value != 0; return RLB_OK; }
-    if (!strcmp(name, "persistent")) { m->use_mega = value != 0; return RLB_OK; }
     if (!strcmp(name, "pdl")) { m->use_pdl = value != 0; return RLB_OK; }
     if (!strcmp(name, "profile")) {
         m->profile = value != 0;

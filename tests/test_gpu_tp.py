@@ -1,6 +1,7 @@
-"""Tensor parallelism on real GPUs (needs two): two processes, one per GPU, shard the model
-through the C ABI, exchange over NCCL and must reproduce the CPU oracle's logits within the
-single-GPU bounds; both ranks must return identical logits."""
+"""Tensor parallelism on real GPUs (needs two, four or eight): one process per GPU shards the
+model through the C ABI, exchanges over NCCL or the fused push exchange and must reproduce the
+CPU oracle's logits within the single-GPU bounds; every rank must return identical logits.
+Cases that need more GPUs than the box has are skipped."""
 import os
 import sys
 import time
@@ -20,7 +21,7 @@ def _device_count():
     return n.value
 
 
-def _worker(rank, world, tmpdir, f16, heads, mode):
+def _worker(rank, world, tmpdir, f16, over, mode, n_prompt):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -28,7 +29,7 @@ def _worker(rank, world, tmpdir, f16, heads, mode):
     from rllama_b200 import synthetic as S
     from helpers import cfg_variant
 
-    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, n_heads=heads, dim=64 * heads, max_seq_len=32)
+    cfg = cfg_variant("tiny", **over)
     cl = Cuda(nth_device=rank)
     ds = DataSettings(cl=cl)
     if f16:
@@ -65,49 +66,74 @@ def _worker(rank, world, tmpdir, f16, heads, mode):
         m.set_tp_mode("push")
     S.load_into(m, cfg)
     m.finalize()
-    prompt = S.synth_tokens(7, cfg["vocab"])
+    prompt = S.synth_tokens(n_prompt, cfg["vocab"])
     c = m.make_caches()
     outs = [m.forward(prompt, 0, c)]
     toks = np.load(os.path.join(tmpdir, "oracle_tokens.npy"))
     for i, t in enumerate(toks):
-        outs.append(m.forward([int(t)], 7 + i, c))
+        outs.append(m.forward([int(t)], n_prompt + i, c))
     c2 = m.make_caches()
     first = m.forward_greedy(prompt, 0, c2)
-    dev_tokens, _ = m.decode_greedy(first, 7, 5, c2)  # graph replays with on-device feedback
+    dev_tokens, _ = m.decode_greedy(first, n_prompt, 5, c2)  # graph replays with on-device feedback
     np.save(os.path.join(tmpdir, "dev_tokens_rank%d.npy" % rank), dev_tokens)
     np.save(os.path.join(tmpdir, "logits_rank%d.npy" % rank), np.stack(outs))
     np.save(os.path.join(tmpdir, "first_rank%d.npy" % rank), np.array([first]))
     cl.flush()
 
 
-@pytest.mark.parametrize("f16,heads,mode", [(False, 4, "nccl"), (True, 4, "nccl"), (True, 3, "nccl"),
-                                            (False, 4, "push"), (True, 4, "push"), (True, 3, "push")])
-def test_tp2_matches_oracle(tmp_path, f16, heads, mode):
-    if _device_count() < 2:
-        pytest.skip("needs two GPUs")
+def _run_tp(tmp_path, world, f16, over, mode, n_prompt):
+    if _device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
     import torch.multiprocessing as mp
     from rllama_b200 import synthetic as S
     from helpers import build_pair, cfg_variant
-    cfg = cfg_variant("tiny", n_layers=2, vocab=2000, n_heads=heads, dim=64 * heads, max_seq_len=32)
+    cfg = cfg_variant("tiny", **over)
     _, orc = build_pair(cfg, f16, with_gpu=False)
-    prompt = S.synth_tokens(7, cfg["vocab"])
+    prompt = S.synth_tokens(n_prompt, cfg["vocab"])
     oc = orc.make_caches()
     want = [orc.forward(prompt, 0, oc)]
     toks = []
     for i in range(4):
         toks.append(int(np.argmax(want[-1])))
-        want.append(orc.forward([toks[-1]], 7 + i, oc))
+        want.append(orc.forward([toks[-1]], n_prompt + i, oc))
     np.save(str(tmp_path / "oracle_tokens.npy"), np.array(toks, dtype=np.int32))
-    mp.spawn(_worker, args=(2, str(tmp_path), f16, heads, mode), nprocs=2, join=True)
-    r0 = np.load(str(tmp_path / "logits_rank0.npy")); r1 = np.load(str(tmp_path / "logits_rank1.npy"))
-    assert np.array_equal(r0, r1)  # every rank holds the same logits, bit for bit
+    mp.spawn(_worker, args=(world, str(tmp_path), f16, over, mode, n_prompt), nprocs=world, join=True)
+    logits = [np.load(str(tmp_path / ("logits_rank%d.npy" % r))) for r in range(world)]
+    for r in range(1, world):
+        assert np.array_equal(logits[0], logits[r])  # every rank holds the same logits, bit for bit
     want = np.stack(want)
     if f16:
-        assert float(np.abs(r0 - want).max()) <= 2e-2
+        assert float(np.abs(logits[0] - want).max()) <= 2e-2
     else:
-        assert float(np.abs(r0 - want).max() / np.abs(want).max()) <= 1e-4
-    assert int(np.load(str(tmp_path / "first_rank0.npy"))[0]) == int(np.load(str(tmp_path / "first_rank1.npy"))[0])
-    d0 = np.load(str(tmp_path / "dev_tokens_rank0.npy")); d1 = np.load(str(tmp_path / "dev_tokens_rank1.npy"))
-    assert np.array_equal(d0, d1)
+        assert float(np.abs(logits[0] - want).max() / np.abs(want).max()) <= 1e-4
+    firsts = [int(np.load(str(tmp_path / ("first_rank%d.npy" % r)))[0]) for r in range(world)]
+    assert len(set(firsts)) == 1
+    dev = [np.load(str(tmp_path / ("dev_tokens_rank%d.npy" % r))) for r in range(world)]
+    for r in range(1, world):
+        assert np.array_equal(dev[0], dev[r])
     if not f16:  # f32: the device loop must follow the oracle's greedy continuation exactly
-        assert d0[:3].tolist() == toks[1:4]
+        assert dev[0][:3].tolist() == toks[1:4]
+
+
+@pytest.mark.parametrize("f16,heads,mode", [(False, 4, "nccl"), (True, 4, "nccl"), (True, 3, "nccl"),
+                                            (False, 4, "push"), (True, 4, "push"), (True, 3, "push")])
+def test_tp2_matches_oracle(tmp_path, f16, heads, mode):
+    _run_tp(tmp_path, 2, f16, dict(n_layers=2, vocab=2000, n_heads=heads, dim=64 * heads, max_seq_len=32), mode, 7)
+
+
+@pytest.mark.parametrize("mode", ["push", "nccl"])
+def test_tp4_7b_width_matches_oracle(tmp_path, mode):
+    """Four ranks at the 7B layer shape (dim 4096, 8 heads and 2752 FFN columns per rank), depth 1: the push
+    exchange runs with its real slice widths and four partial sums per element; the 64-token prompt takes the
+    tensor-core GEMM with the all-reduce after wo and w2."""
+    _run_tp(tmp_path, 4, True, dict(dim=4096, n_heads=32, ffn=11008, n_layers=1, vocab=2048, max_seq_len=96), mode, 64)
+
+
+def test_tp8_uneven_heads_matches_oracle(tmp_path):
+    """Eight ranks at the 30B layer shape: 52 heads split 7,7,7,7,6,6,6,6 (rllama concatenates Meta's shards on
+    these axes, src/transformer.rs:594-617), rows of 6656 elements, eight partial sums per element."""
+    _run_tp(tmp_path, 8, True, dict(dim=6656, n_heads=52, ffn=17920, n_layers=1, vocab=2048, max_seq_len=96), "push", 64)
+
+
+def test_tp8_f32_matches_oracle(tmp_path):
+    _run_tp(tmp_path, 8, False, dict(dim=1024, n_heads=8, ffn=2752, n_layers=2, vocab=2048, max_seq_len=48), "push", 20)
