@@ -112,6 +112,16 @@ int rlb_matrix_mul_inplace_transposed(rlb_tensor* dst, const rlb_tensor* src, co
 int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
                          int32_t heads, int32_t max_seq_len, int32_t pos, int32_t n_split);
 
+/* The same per-head attention for a multi-token call (the prefill half of Attention::forward,
+ * src/transformer.rs:727-781, with the causal mask of Tensor::full_triu, src/tensor.rs:496-508):
+ *   q    n x (heads*head_dim) f32, already rotated; row i attends to positions 0..start_pos+i
+ *   out  n x (heads*head_dim) in the cache dtype, no row padding
+ * f16 caches with head_dim 64 or 128 and n >= 32 run on the tensor cores (q and the softmax
+ * weights split into two f16 halves, so no rounding point is added); tensor_cores = 0 keeps
+ * the call on the CUDA-core kernel (for comparisons).                                    */
+int rlb_attention_prefill(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache,
+                          int32_t heads, int32_t max_seq_len, int32_t start_pos, int32_t tensor_cores);
+
 /* rlb_attention_decode without any allocation (no counterpart in the reference). For hosts
  * that cannot let the library allocate on the token path: a server whose HBM is already
  * split between weights and KV caches, or a latency-critical thread that must not stall the
@@ -155,6 +165,13 @@ typedef struct rlb_model_params {
                              per-layer matrices and the KV cache are f16; else f32      */
     int32_t tp_rank;      /* tensor-parallel rank of this process, 0 <= rank < tp_size   */
     int32_t tp_size;      /* 1, 2, 4 or 8; heads and FFN columns are split               */
+    int32_t has_percentage_to_gpu;  /* 0: every layer is resident in HBM (the default, 1.0)  */
+    float percentage_to_gpu;  /* DataSettings::percentage_to_gpu (src/transformer.rs:91-103,
+                             --percentage-to-gpu): clamped to [0, 1], NaN -> 0; layer i is
+                             resident in HBM iff i <= round(p * (n_layers - 1)) (:262-274).
+                             There is no CPU path: the other layers' matrices stay in pinned
+                             host memory and are copied into one HBM staging buffer, layer by
+                             layer, inside every forward call (same kernels, same results). */
 } rlb_model_params;
 
 /* Transformer::from_unpickled (src/transformer.rs:242-326), construction half.        */
@@ -299,7 +316,7 @@ int rlb_sampler_candidates(rlb_sampler* s, const float* logits, int32_t vocab, c
 
 /* Tuning and inspection. Options: "graph" (replay the decode step as a CUDA graph, default 1),
  * "stream_gemv" (bulk-copy staged GEMV kernels, default 1), "pdl" (programmatic dependent launch,
- * default 1), "profile" (time every kernel class of the decode step). Statistics: "kernels_per_step", "attn_split", "local_heads",
+ * default 1), "profile" (time every kernel class of the decode step). Statistics: "kernels_per_step", "attn_split", "local_heads", "layers_on_gpu",
  * "first_head", "local_ffn", "local_vocab", "vocab_size", "ffn_dim", "prof_steps", "prof_ms_<qkv|attn|wo|w13|w2|head|argmax|comm>". */
 int rlb_model_set_option(rlb_model* m, const char* name, int64_t value);
 int rlb_model_get_stat(rlb_model* m, const char* name, double* value);

@@ -41,7 +41,7 @@ class Cuda {
 struct DataSettings {
     Cuda* cl = nullptr;
     bool force_f16_ = false;
-    float percentage_to_gpu_ = 1.0f;  // kept for surface compatibility: there is no CPU path
+    float percentage_to_gpu_ = 1.0f;  // layers beyond round(p * (n_layers - 1)) wait in pinned host memory (no CPU path)
     DataSettings force_f16() const { DataSettings d = *this; d.force_f16_ = true; return d; }
     DataSettings percentage_to_gpu(float p) const {
         DataSettings d = *this;
@@ -83,6 +83,7 @@ class Transformer {
         p.dim = dim; p.n_layers = n_layers; p.n_heads = n_heads; p.ffn_dim = ffn_dim; p.vocab_size = vocab_size;
         p.max_seq_len = max_seq_len; p.norm_eps = (float)eps; p.force_f16 = data_settings.force_f16_ ? 1 : 0;
         p.tp_rank = tp_rank; p.tp_size = tp_size;
+        p.has_percentage_to_gpu = 1; p.percentage_to_gpu = data_settings.percentage_to_gpu_;
         check(rlb_model_create(data_settings.cl->handle(), &p, &h_));
     }
     ~Transformer() { rlb_model_free(h_); }
@@ -163,6 +164,7 @@ inline std::unique_ptr<Transformer> Transformer::from_unpickled(int dim, int n_l
     rlb_model_params p{};
     p.dim = dim; p.n_layers = n_layers; p.n_heads = n_heads; p.max_seq_len = max_seq_len; p.norm_eps = (float)eps;
     p.force_f16 = data_settings.force_f16_ ? 1 : 0; p.tp_rank = tp_rank; p.tp_size = tp_size;
+    p.has_percentage_to_gpu = 1; p.percentage_to_gpu = data_settings.percentage_to_gpu_;
     std::unique_ptr<Transformer> t(new Transformer());
     check(rlb_model_from_llama_source(data_settings.cl->handle(), data_source.handle(), &p, &t->h_));
     double v = 0;

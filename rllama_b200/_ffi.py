@@ -18,7 +18,7 @@ EXPORTS = [
     "rlb_ctx_create", "rlb_ctx_destroy", "rlb_ctx_flush", "rlb_ctx_kernel_launches",
     "rlb_tensor_upload", "rlb_tensor_zeros", "rlb_tensor_wait", "rlb_tensor_download", "rlb_event_wait", "rlb_tensor_free",
     "rlb_copy_inplace", "rlb_transpose_from", "rlb_hadamard_product_inplace", "rlb_silu_inplace",
-    "rlb_matrix_mul_inplace_transposed", "rlb_attention_decode", "rlb_attention_decode_static",
+    "rlb_matrix_mul_inplace_transposed", "rlb_attention_decode", "rlb_attention_decode_static", "rlb_attention_prefill",
     "rlb_model_create", "rlb_model_set_tensor", "rlb_model_finalize", "rlb_model_free",
     "rlb_tp_nccl_unique_id", "rlb_tp_nccl_init", "rlb_tp_peer_export", "rlb_tp_peer_import", "rlb_tp_set_mode",
     "rlb_caches_create", "rlb_caches_true_clone", "rlb_caches_shift_left", "rlb_caches_free", "rlb_caches_read",
@@ -49,6 +49,7 @@ class ModelParams(ctypes.Structure):
         ("ffn_dim", ctypes.c_int32), ("vocab_size", ctypes.c_int32), ("max_seq_len", ctypes.c_int32),
         ("norm_eps", ctypes.c_float), ("force_f16", ctypes.c_int32),
         ("tp_rank", ctypes.c_int32), ("tp_size", ctypes.c_int32),
+        ("has_percentage_to_gpu", ctypes.c_int32), ("percentage_to_gpu", ctypes.c_float),
     ]
 
 
@@ -78,6 +79,7 @@ def lib():
         "rlb_silu_inplace": [vp], "rlb_matrix_mul_inplace_transposed": [vp, vp, vp],
         "rlb_attention_decode": [vp, vp, vp, vp, i32, i32, i32, i32],
         "rlb_attention_decode_static": [vp, vp, vp, vp, i32, i32, i32, i32],
+        "rlb_attention_prefill": [vp, vp, vp, vp, i32, i32, i32, i32],
         "rlb_model_create": [vp, P(ModelParams), P(vp)],
         "rlb_model_set_tensor": [vp, ci, i32, vp, i64, i64, i64, ci],
         "rlb_model_finalize": [vp], "rlb_model_free": [vp],

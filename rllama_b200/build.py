@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "librllama_b200.so")
 CLI = os.path.join(HERE, "bin", "rllama-b200")
-SOURCES = ["context.cu", "gemv.cu", "gemv_stream.cu", "attention.cu", "elementwise.cu", "gemm.cu", "gemm_tc.cu", "model.cu", "tp.cu", "loader.cu", "host.cu"]
+SOURCES = ["context.cu", "gemv.cu", "gemv_stream.cu", "attention.cu", "attention_tc.cu", "elementwise.cu", "gemm.cu", "gemm_tc.cu", "model.cu", "tp.cu", "loader.cu", "host.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]

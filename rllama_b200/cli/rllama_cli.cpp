@@ -5,7 +5,8 @@
 // the whole prompt at position 0, then one token per call at position len-1), same colours, same
 // stop rule ("</s>"), same interactive mode, same timing lines at the end. Differences:
 //  * the model lives on the device: `--cuda-device` (alias `--opencl-device`) picks it,
-//    `--percentage-to-gpu` is accepted and ignored (every layer is resident in HBM);
+//    `--percentage-to-gpu <p>`: layer i is resident in HBM iff i <= round(p * (n_layers - 1)), as in the reference;
+//    there is no CPU path, so the other layers wait in pinned host memory and are copied to the GPU inside every forward;
 //  * `--f16` alone selects f16 weights and caches (the reference's OpenCL build forces f16);
 //  * `--seed` (no counterpart) seeds the sampler's draw, which the reference takes from thread_rng;
 //  * `--inference-server` runs the HTTP server of inference_server.hpp (the reference: rocket).
@@ -67,7 +68,7 @@ void print_help() {
         "      --interactive-system-prompt <TEXT>\n      --interactive-stop <TEXT> (repeatable)\n"
         "      --interactive-prompt-postfix <TEXT>\n      --interactive-prompt-prefix <TEXT>\n      --start-interactive\n"
         "      --max-seq-len <N>\n      --temperature <T>\n      --top-p <P>\n      --top-k <K>\n      --repetition-penalty <R>\n"
-        "      --max-threads <N>\n      --f16\n      --cuda-device <N> (alias --opencl-device)\n      --percentage-to-gpu <P> (ignored)\n"
+        "      --max-threads <N>\n      --f16\n      --cuda-device <N> (alias --opencl-device)\n      --percentage-to-gpu <P>\n"
         "      --seed <N>\n      --inference-server\n      --inference-server-port <PORT>\n      --inference-server-host <HOST>\n"
         "      --inference-server-max-concurrent-inferences <N>\n      --inference-server-api-path <PATH>\n"
         "      --inference-server-prompt-cache-size <N>\n      --inference-server-exit-after-one-query\n  -h, --help");
@@ -417,6 +418,8 @@ static void run(const Cli& cli) {
     params.force_f16 = cli.f16 ? 1 : 0;
     params.tp_rank = 0;
     params.tp_size = 1;
+    params.has_percentage_to_gpu = 1;
+    params.percentage_to_gpu = cli.percentage_to_gpu.value_or(1.0f);  // src/rllama_main.rs:160
     pln("Loading embeddings from " + cli.model_path + "...");
     pln("Loading transformer weights from " + cli.model_path + "...");
     rlb_model* model = nullptr;

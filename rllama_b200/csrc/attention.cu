@@ -667,6 +667,7 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
     const int vec = cache_dtype == RLB_F16 ? 8 : 4;
     if (a.hd % 8 != 0 || (a.hd / 8) % vec != 0 || a.hd / vec > kThreads)
         return rlb_fail(RLB_ERR_INVALID, "attention: head_dim %d is not supported", a.hd);
+    if (a.allow_tc && attn_prefill_tc_supported(cache_dtype, a)) return launch_attn_prefill_tc(ctx, a, a.err);
     static const bool use_tiled = getenv("RLB_ATTN_TILED") == nullptr || atoi(getenv("RLB_ATTN_TILED")) != 0;
     if (use_tiled && a.n >= 8 && (a.hd == 64 || a.hd == 128) && a.q_ld % 4 == 0) {
         const size_t smem = sizeof(float) * ((size_t)kQB * (a.hd + 4) + (size_t)kTB * (a.hd + 4) + (size_t)kTB * a.hd + (size_t)kQB * (kTB + 1));

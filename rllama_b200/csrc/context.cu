@@ -349,3 +349,30 @@ extern "C" int rlb_attention_decode(rlb_tensor* out, const rlb_tensor* q, const 
     RLB_CUDA(cudaEventRecord(out->ready, ctx->stream));
     return RLB_OK;
 }
+
+// The per-head part of Attention::forward for a multi-token call as a standalone op: row i of q attends to
+// positions 0 .. start_pos + i of the caches (the mask of Tensor::full_triu, src/tensor.rs:496-508).
+extern "C" int rlb_attention_prefill(rlb_tensor* out, const rlb_tensor* q, const rlb_tensor* kcache, const rlb_tensor* vcache, int32_t heads,
+                                     int32_t max_seq_len, int32_t start_pos, int32_t tensor_cores) {
+    RLB_TRY(same_ctx(out, q));
+    RLB_TRY(same_ctx(out, kcache));
+    RLB_TRY(same_ctx(out, vcache));
+    const int64_t n = q->rows, hd = kcache->cols;
+    if (heads < 1 || max_seq_len < 1 || n < 1 || start_pos < 0 || start_pos + n > max_seq_len)
+        return rlb_fail(RLB_ERR_INVALID, "attention_prefill: bad heads %d, max_seq_len %d, start_pos %d or %lld rows", heads, max_seq_len, start_pos,
+                        (long long)n);
+    if (kcache->cap != hd || vcache->cap != hd || vcache->cols != hd || kcache->rows != (int64_t)heads * max_seq_len ||
+        vcache->rows != kcache->rows || kcache->dtype != vcache->dtype)
+        return rlb_fail(RLB_ERR_INVALID, "attention_prefill: caches must be (heads*max_seq_len) x head_dim without row padding");
+    if (q->dtype != RLB_F32 || q->cols != (int64_t)heads * hd) return rlb_fail(RLB_ERR_INVALID, "attention_prefill: q must be n x heads*head_dim f32");
+    if (out->dtype != kcache->dtype || out->rows != n || out->cols != q->cols || out->cap != out->cols)
+        return rlb_fail(RLB_ERR_INVALID, "attention_prefill: out must be n x heads*head_dim in the cache dtype, without row padding");
+    OP_PROLOGUE(ctx, out);
+    AttnPrefillArgs a;
+    a.q = (const float*)q->d; a.q_ld = q->cap; a.kcache = kcache->d; a.vcache = vcache->d; a.out = out->d;
+    a.n = (int)n; a.start_pos = start_pos; a.heads = heads; a.hd = (int)hd; a.max_seq = max_seq_len;
+    a.allow_tc = tensor_cores != 0;
+    RLB_TRY(launch_attn_prefill(ctx, kcache->dtype, a));
+    RLB_CUDA(cudaEventRecord(out->ready, ctx->stream));
+    return RLB_OK;
+}

@@ -1,24 +1,38 @@
 // Prefill contraction on the 5th-generation tensor cores: C[n][M] = X[n][K] * W[M][K]^T for f16
 // operands with f32 accumulation -- rllama's batched Tensor::matrix_mul_transposed
 // (src/tensor.rs:999-1025, f16 branch :1476-1666; OpenCL kernel matrix_mul_transposed_f16,
-// src/tensor_opencl_support.rs:512-557), the only dense contraction on the path.
+// src/tensor_opencl_support.rs:512-557), the dense contraction of the projections.
 //
-// One CTA computes a 128 (weight rows) x BN (tokens) tile:
-//  * operands arrive by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the
-//    tensor) into a shared-memory ring of 4 to 8 stages (192 KB); one thread issues the loads;
-//  * when the output has few tiles (short prompts, wo / w2) K is split over blockIdx.z and a
-//    second kernel adds the partial tiles in a fixed order;
-//  * one thread issues tcgen05.mma (kind::f16, M 128, N BN, K 16 per instruction, four per
-//    64-column stage) with the accumulator in tensor memory; tcgen05.commit releases a ring
-//    slot when the MMAs that read it have finished;
-//  * four warps read the accumulator back with tcgen05.ld (each warp owns 32 TMEM lanes = 32
-//    weight rows), round to f16 where the reference rounds the GEMM result, and store
-//    token-major so that a warp writes 128 contiguous bytes per token.
-// Products of f16 values are exact in f32; only the summation order differs from the
-// reference's 8-lane FMA scheme.
+// One persistent kernel, one CTA per SM. A tile is 128 tokens x 256 weight rows: the tokens are the
+// MMA's M (tensor-memory lanes), the weight rows its N (tensor-memory columns), so a thread of the
+// epilogue owns one token and reads consecutive weight rows -- consecutive addresses of the
+// row-major output.
+//  * Work is handed out per (tile, 64-column k-block). The first floor(tiles / CTAs) * CTAs tiles go
+//    round-robin to the CTAs as whole tiles (neighbouring CTAs work on neighbouring tiles, so the
+//    weight rows a group of token tiles shares are read from HBM once and then from L2); the k-blocks
+//    of the remaining tiles are dealt out in equal contiguous runs over all CTAs, so every SM streams the
+//    same number of bytes whatever the shape (short prompts, few tiles: this is a K split). A run that
+//    does not cover a tile's whole K range leaves an f32 partial tile in scratch memory; a second kernel
+//    adds the partial tiles of a tile in k order (fixed by the schedule, so results never depend on
+//    timing) and applies the output rounding.
+//  * Operands arrive by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the tensor)
+//    into a 192 KB shared-memory ring; one thread issues the loads and runs ahead across tiles.
+//  * One thread issues tcgen05.mma (kind::f16, M 128, N 256, K 16 per instruction) into one of two
+//    accumulators in tensor memory (2 x 256 columns): the next tile's main loop runs while four warps
+//    read the finished accumulator back with tcgen05.ld, round to f16 where the reference rounds the
+//    GEMM result, and store 64 contiguous bytes per thread and step.
+// Products of f16 values are exact in f32; only the summation order differs from the reference's
+// 8-lane FMA scheme.
 //
-// Every mbarrier wait is bounded; on a timeout the kernel raises the error word and still
-// releases its tensor memory before returning.
+// TF32 = true is the f32 form for weights whose values are f16-representable (what the checkpoint
+// loader produces): operands are 32-bit, kind::tf32, 32 K columns (still 128 bytes) per stage. A weight
+// with at most 11 significant bits is exact in TF32; the activations are not, so they are split into
+// x = hi + lo (hi = x rounded to TF32, lo = x - hi), a stage carries both halves next to ONE copy of the
+// weight tile, and every k-block is multiplied twice, hi W and lo W, into the same accumulator: all
+// products are exact in f32 and what is dropped of lo is below 2^-21 of x.
+//
+// Every mbarrier wait is bounded; on a timeout the kernel raises the error word and still releases its
+// tensor memory before returning.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -26,14 +40,15 @@
 
 namespace {
 
-constexpr int BM = 128;       // weight rows per tile (MMA M)
-constexpr int BK = 64;        // K columns per stage: 128 bytes of f16 = one swizzle span
-constexpr int kMaxStages = 8;
-constexpr int kRingBytes = 192 * 1024;  // shared memory given to the operand ring
-// stages that fit the ring for a token tile of BN rows (a weight tile is always 128 x 64 f16)
-constexpr int stages_for(int bn) { return (kRingBytes / (BM * BK * 2 + bn * BK * 2)) < kMaxStages ? (kRingBytes / (BM * BK * 2 + bn * BK * 2)) : kMaxStages; }
+constexpr int TM = 128;       // tokens per tile (MMA M)
+constexpr int TN = 256;       // weight rows per tile (MMA N)
+constexpr int BK = 64;        // K columns per stage in f16 (128 bytes = one swizzle span)
+constexpr int kRingBytes = 192 * 1024;
 constexpr int kTcThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t X_BYTES = TM * 128;   // one activation tile of a stage
+constexpr uint32_t W_BYTES = TN * 128;
+constexpr size_t kSlabFloats = (size_t)TM * TN;   // one partial tile
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,6 +57,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -52,7 +70,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
         : "memory");
     return ok;
 }
-// Bounded wait; false when it ran out (the error word is raised).
+// Bounded wait; false when it ran out (the error word is raised) or the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead, int* err) {
     for (uint32_t i = 0; i < kWaitLimit; i++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -79,66 +97,119 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                         // 128-byte swizzle
     return d;
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if (TF32)
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <typename OT> __device__ __forceinline__ OT out_cast(float v);
-template <> __device__ __forceinline__ float out_cast<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half out_cast<__half>(float v) { return __float2half_rn(v); }
+// ---- the schedule --------------------------------------------------------------------------------
+struct Sched {
+    int n_mt, n_nt, nkb;   // token tiles, weight-row tiles, k-blocks per tile
+    int whole;             // tiles handed out whole, round-robin (a multiple of the grid size)
+    int rest;              // remaining tiles, dealt out by k-block
+};
+__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid) {
+    Sched s;
+    s.n_mt = (n + TM - 1) / TM; s.n_nt = (M + TN - 1) / TN; s.nkb = nkb;
+    const int tiles = s.n_mt * s.n_nt;
+    s.whole = tiles / grid * grid;
+    s.rest = tiles - s.whole;
+    return s;
+}
+// First k-block unit of CTA c's run over the remaining tiles (units are numbered tile-major).
+__host__ __device__ inline long long rest_begin(const Sched& s, int c, int grid) { return (long long)c * s.rest * s.nkb / grid; }
 
-// blockIdx.z selects a K range (split-K): with more than one split every split stores its f32
-// partial tile into its own [n][ldc] slab of C (slab stride `split_stride` elements) and a second
-// kernel adds the slabs in a fixed order, so the result does not depend on timing.
-//
-// TF32 = true is the f32 form for weights whose values are f16-representable (what the checkpoint
-// loader produces): operands are 32-bit, kind::tf32, 32 K columns (still 128 bytes) per stage. A weight
-// with at most 11 significant bits is exact in TF32; the activations are not, so the caller passes them
-// split into x = hi + lo (hi = x rounded to TF32, lo = x - hi) and every k-block is multiplied twice,
-// W x hi and W x lo, into the same accumulator: all products are exact in f32 and what is dropped of lo is
-// below 2^-21 of x.
-template <int BN, typename OT, bool TF32>
-__global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                             const __grid_constant__ CUtensorMap tm_x,
-                                                             const __grid_constant__ CUtensorMap tm_x2, OT* __restrict__ C, int64_t ldc,
-                                                             int n, int Mrows, int K, int round_out, int64_t split_stride, int* err) {
-    constexpr int kStages = stages_for(BN);
-    constexpr int BKE = TF32 ? BK / 2 : BK;   // K columns of a stage (128 bytes either way)
-    constexpr int PASSES = TF32 ? 2 : 1;
-    constexpr uint32_t A_BYTES = BM * BK * 2;
-    constexpr uint32_t B_BYTES = BN * BK * 2;
-    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+// One piece of work: k-blocks [kb0, kb1) of a tile. `slot` < 0: the piece covers the whole K range and
+// its result goes straight to the output; otherwise it is partial tile number `slot` (0 or 1) of this CTA.
+struct Piece { int tile, kb0, kb1, slot; };
+struct PieceIter {
+    Sched s; int cta, grid;
+    int t;                  // next whole tile
+    long long u, u0, u1;    // position in, and bounds of, this CTA's run over the remaining tiles
+    __device__ PieceIter(const Sched& s_, int cta_, int grid_) : s(s_), cta(cta_), grid(grid_) {
+        t = cta;
+        u0 = rest_begin(s, cta, grid); u1 = rest_begin(s, cta + 1, grid); u = u0;
+    }
+    __device__ bool next(Piece& p) {
+        if (t < s.whole) { p.tile = t; p.kb0 = 0; p.kb1 = s.nkb; p.slot = -1; t += grid; return true; }
+        if (u >= u1) return false;
+        const int j = (int)(u / s.nkb);
+        p.tile = s.whole + j;
+        p.kb0 = (int)(u - (long long)j * s.nkb);
+        const long long left = u1 - u;
+        p.kb1 = (int)(p.kb0 + left < s.nkb ? p.kb0 + left : s.nkb);
+        p.slot = (p.kb0 == 0 && p.kb1 == s.nkb) ? -1 : (u == u0 ? 0 : 1);
+        u += p.kb1 - p.kb0;
+        return true;
+    }
+};
+
+template <typename OT> struct OutPack;
+template <> struct OutPack<float> {
+    static __device__ __forceinline__ void store16(float* dst, const float (&v)[16], bool vec, int valid_cols) {
+        if (vec && valid_cols >= 16) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < valid_cols) dst[j] = v[j];
+        }
+    }
+};
+template <> struct OutPack<__half> {
+    static __device__ __forceinline__ void store16(__half* dst, const float (&v)[16], bool vec, int valid_cols) {
+        if (vec && valid_cols >= 16) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                w[j] = (uint32_t)__half_as_ushort(__float2half_rn(v[2 * j])) | ((uint32_t)__half_as_ushort(__float2half_rn(v[2 * j + 1])) << 16);
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < valid_cols) dst[j] = __float2half_rn(v[j]);
+        }
+    }
+};
+
+template <typename OT, bool TF32>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x,
+                                                                const __grid_constant__ CUtensorMap tm_x2,
+                                                                const __grid_constant__ CUtensorMap tm_w, OT* __restrict__ C, int64_t ldc,
+                                                                int n, int Mrows, int K, int round_out, float* __restrict__ part, int* err) {
+    constexpr int BKE = TF32 ? BK / 2 : BK;                      // K columns of a stage (128 bytes either way)
+    constexpr int NX = TF32 ? 2 : 1;                             // activation tiles per stage (hi, lo)
+    constexpr uint32_t STAGE_BYTES = NX * X_BYTES + W_BYTES;
+    constexpr int kStages = kRingBytes / STAGE_BYTES;            // 4 (f16), 3 (tf32)
+    constexpr uint32_t TMEM_COLS = 2 * TN;
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t full_bar[kStages];
     __shared__ __align__(8) uint64_t empty_bar[kStages];
-    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int dead_flag;
     volatile int* dead = &dead_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM;  // first weight row of the tile
-    const int n0 = blockIdx.y * BN;  // first token of the tile
-    const int nkb_total = (K + BKE - 1) / BKE;
-    const int per_split = (nkb_total + (int)gridDim.z - 1) / (int)gridDim.z;
-    const int kb_first = (int)blockIdx.z * per_split;
-    const int nkb = max(0, min(nkb_total, kb_first + per_split) - kb_first);  // k-blocks of this split
-    C += (int64_t)blockIdx.z * split_stride;
+    const int nkb = (K + BKE - 1) / BKE;
+    const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x);
 
     if (threadIdx.x == 0) {
         dead_flag = 0;
@@ -146,10 +217,13 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&done_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {  // one warp allocates the accumulator's tensor memory
+    if (warp == 0) {  // one warp allocates the accumulators' tensor memory
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS)
                      : "memory");
@@ -161,70 +235,103 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const uint32_t tmem_base = tmem_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer ----------------
-        for (int it = 0; it < nkb * PASSES; it++) {
-            const int s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1u;
-            const int kb = it / PASSES;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
-            unsigned char* a_s = tiles + (size_t)s * STAGE_BYTES;
-            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a_s, &tm_w, (kb_first + kb) * BKE, m0, &full_bar[s]);  // (second pass: the same tile again, from L2)
-            tma_load_2d(a_s + A_BYTES, (PASSES == 2 && (it & 1)) ? &tm_x2 : &tm_x, (kb_first + kb) * BKE, n0, &full_bar[s]);
+        // ---------------- TMA producer: runs ahead of the MMAs across pieces ----------------
+        PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
+        Piece p;
+        uint32_t cnt = 0;
+        bool ok = true;
+        while (ok && it.next(p)) {
+            const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
+            for (int kb = p.kb0; kb < p.kb1; kb++, cnt++) {
+                const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) { ok = false; break; }
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(st, &tm_x, kb * BKE, mt * TM, &full_bar[s]);
+                if (TF32) tma_load_2d(st + X_BYTES, &tm_x2, kb * BKE, mt * TM, &full_bar[s]);
+                tma_load_2d(st + NX * X_BYTES, &tm_w, kb * BKE, nt * TN, &full_bar[s]);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        // instruction descriptor: f32 accumulator, f16 A and B, both K-major, N = BN, M = 128
+        // instruction descriptor: f32 accumulator, A and B both K-major, N = TN, M = TM
         // (operand format field: 0 = f16, 2 = tf32, for A at bit 7 and B at bit 10)
-        const uint32_t idesc = (1u << 4) | (TF32 ? ((2u << 7) | (2u << 10)) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (TF32 ? ((2u << 7) | (2u << 10)) : 0u) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+        PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
+        Piece p;
+        uint32_t cnt = 0, piece = 0;
         bool ok = true;
-        for (int kb = 0; kb < nkb * PASSES && ok; kb++) {
-            const int s = kb % kStages;
-            const uint32_t ph = (kb / kStages) & 1u;
-            ok = mbar_wait(&full_bar[s], ph, dead, err);
+        while (ok && it.next(p)) {
+            const uint32_t b = piece & 1u;
+            ok = mbar_wait(&acc_empty[b], ((piece >> 1) & 1u) ^ 1u, dead, err);  // the epilogue has drained this accumulator
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-            const uint32_t b_addr = a_addr + A_BYTES;
+            const uint32_t d = tmem_base + b * TN;
+            for (int kb = p.kb0; kb < p.kb1; kb++, cnt++) {
+                const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
+                ok = mbar_wait(&full_bar[s], ph, dead, err);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t x_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint32_t w_addr = x_addr + NX * X_BYTES;
 #pragma unroll
-            for (int k = 0; k < BK / 16; k++) {
-                // one instruction covers 32 bytes of K (16 f16 or 8 tf32 columns) along the swizzled row
-                if (TF32) umma_tf32(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
-                else umma_f16(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+                for (int pass = 0; pass < NX; pass++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        // one instruction covers 32 bytes of K (16 f16 or 8 tf32 columns) along the swizzled row
+                        umma<TF32>(d, umma_desc(x_addr + pass * X_BYTES + k * 32), umma_desc(w_addr + k * 32), idesc,
+                                   (kb != p.kb0 || pass != 0 || k != 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);  // the slot is free once these MMAs have read it
             }
-            umma_commit(&empty_bar[s]);  // the slot is free once these MMAs have read it
+            if (ok) umma_commit(&acc_full[b]);
+            piece++;
         }
-        umma_commit(&done_bar);
-    }
-
-    // ---------------- epilogue: warps 2..5, one TMEM lane quarter each ----------------
-    if (warp >= 2) {
-        const bool ok = mbar_wait(&done_bar, 0, dead, err);
-        __syncwarp();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    } else if (warp >= 2) {
+        // ---------------- epilogue: warps 2..5, one TMEM lane quarter (32 tokens) each ----------------
         const int q = warp & 3;
-        const int row = m0 + q * 32 + lane;
-        if (ok) {
+        PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
+        Piece p;
+        uint32_t piece = 0;
+        const bool vec_c = ((ldc * (int64_t)sizeof(OT)) % 16 == 0) && (((uintptr_t)C & 15) == 0);
+        while (it.next(p)) {
+            const uint32_t b = piece & 1u;
+            const bool ok = mbar_wait(&acc_full[b], (piece >> 1) & 1u, dead, err);
+            __syncwarp();
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
+            const int token = mt * TM + q * 32 + lane;
+            const int col_base = nt * TN;
+            float* slab = p.slot >= 0 ? part + ((size_t)blockIdx.x * 2 + p.slot) * kSlabFloats + (size_t)(q * 32 + lane) * TN : nullptr;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = 0; c0 < TN; c0 += 16) {
+                if (col_base + c0 >= Mrows) break;  // (uniform over the warp)
                 uint32_t r[16];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * TN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                       "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float v[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int token = n0 + c0 + j;
-                    if (token < n && row < Mrows) {
-                        float v = nkb > 0 ? __uint_as_float(r[j]) : 0.f;
-                        if (round_out) v = __half2float(__float2half_rn(v));
-                        C[(int64_t)token * ldc + row] = out_cast<OT>(v);
+                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+                if (slab) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(slab + c0)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else if (token < n) {
+                    if (round_out) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) v[j] = __half2float(__float2half_rn(v[j]));
                     }
+                    OutPack<OT>::store16(C + (int64_t)token * ldc + col_base + c0, v, vec_c, Mrows - (col_base + c0));
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+            piece++;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -235,17 +342,46 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     }
 }
 
-// Second pass of split-K: out[i][j] = cast(round?(sum over slabs in slab order)).
+// Second pass for the tiles that were dealt out by k-block: out = cast(round?(sum of the tile's partial tiles
+// in k order)). grid (remaining tiles, 8 row groups of 16 tokens).
 template <typename OT>
-__global__ void splitk_reduce_kernel(const float* __restrict__ part, int64_t slab_stride, int splits, int64_t ld_part, OT* __restrict__ out,
-                                     int64_t ldc, int n, int M, int round_out) {
-    const int64_t total = (int64_t)n * M;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / M, c = i - r * M;
-        float v = 0.f;
-        for (int z = 0; z < splits; z++) v += part[z * slab_stride + r * ld_part + c];
-        if (round_out) v = __half2float(__float2half_rn(v));
-        out[r * ldc + c] = out_cast<OT>(v);
+__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ part, OT* __restrict__ C, int64_t ldc, int n, int Mrows,
+                                                            int nkb, int grid, int round_out) {
+    const Sched s = make_sched(n, Mrows, nkb, grid);
+    const int j = blockIdx.x;
+    const long long u_first = (long long)j * s.nkb, u_last = u_first + s.nkb;
+    // the CTAs whose runs meet this tile: c_lo is the last one that starts at or before the tile's first unit
+    int c_lo = (int)(u_first * grid / ((long long)s.rest * s.nkb));
+    if (c_lo > grid - 1) c_lo = grid - 1;
+    while (c_lo + 1 < grid && rest_begin(s, c_lo + 1, grid) <= u_first) c_lo++;
+    while (c_lo > 0 && rest_begin(s, c_lo, grid) > u_first) c_lo--;
+    int c_hi = c_lo;  // inclusive
+    while (c_hi + 1 < grid && rest_begin(s, c_hi + 1, grid) < u_last) c_hi++;
+    if (c_lo == c_hi) return;  // one CTA computed the whole tile and stored it itself
+    const int tile = s.whole + j;
+    const int nt = tile / s.n_mt, mt = tile - nt * s.n_mt;
+    const int row0 = blockIdx.y * 16;
+    for (int e = threadIdx.x; e < 16 * (TN / 4); e += 256) {
+        const int rr = row0 + e / (TN / 4), c4 = (e % (TN / 4)) * 4;
+        const int token = mt * TM + rr, col = nt * TN + c4;
+        if (token >= n || col >= Mrows) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = c_lo; c <= c_hi; c++) {
+            const long long b = rest_begin(s, c, grid);
+            if (rest_begin(s, c + 1, grid) <= b) continue;  // a CTA without units
+            const int slot = (b >= u_first) ? 0 : 1;        // the piece starts the CTA's run, or follows a tile boundary inside it
+            const float4 t = *reinterpret_cast<const float4*>(part + ((size_t)c * 2 + slot) * kSlabFloats + (size_t)rr * TN + c4);
+            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+        }
+        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            if (round_out) v[q] = __half2float(__float2half_rn(v[q]));
+            if (col + q < Mrows) {
+                if (sizeof(OT) == 4) reinterpret_cast<float*>(C)[(int64_t)token * ldc + col + q] = v[q];
+                else reinterpret_cast<__half*>(C)[(int64_t)token * ldc + col + q] = __float2half_rn(v[q]);
+            }
+        }
     }
 }
 
@@ -276,60 +412,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int
     return RLB_OK;
 }
 
-// Few output tiles: split K so that most SMs stream weights.
-int pick_splits(const rlb_ctx* ctx, int tiles, int nkb) {
-    int splits = 1;
-    if (tiles * 5 < ctx->sm_count * 3) {
-        splits = (ctx->sm_count + tiles - 1) / tiles;
-        if (splits > 8) splits = 8;
-        while (splits > 1 && nkb / splits < 8) splits--;
-    }
-    return splits;
-}
-
-// scratch_off: bytes of the context's GEMM scratch the caller already uses (the split activations).
-template <int BN, typename OT, bool TF32>
-int launch_bn(rlb_ctx* ctx, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tx2, OT* C, int64_t ldc, int n, int M, int K,
-              int round_out, int* err, size_t scratch_off) {
-    const size_t smem = (size_t)stages_for(BN) * (BM * BK * 2 + BN * BK * 2) + 1024;
-    dim3 grid((M + BM - 1) / BM, (n + BN - 1) / BN, 1);
-    const int splits = pick_splits(ctx, (int)(grid.x * grid.y), (K + BK - 1) / BK * (TF32 ? 2 : 1));
-    if (splits == 1) {
-        auto kern = gemm_tc_kernel<BN, OT, TF32>;
-        static std::atomic<uint64_t> set{0};
-        if (!attr_done(set, ctx->device)) {
-            RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_mark(set, ctx->device);
-        }
-        kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, C, ldc, n, M, K, round_out, 0, err);
-        RLB_LAUNCH_CHECK();
-        count_launch(ctx);
-        return RLB_OK;
-    }
-    // slabs of f32 partial tiles in the context's scratch
-    const size_t need = scratch_off + (size_t)splits * n * M * sizeof(float);
-    if (need > ctx->gemm_scratch_bytes) return rlb_fail(RLB_ERR_STATE, "gemm: scratch of %zu bytes was not reserved", need);
-    float* part = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + scratch_off);
-    auto kern = gemm_tc_kernel<BN, float, TF32>;
-    static std::atomic<uint64_t> set{0};
-    if (!attr_done(set, ctx->device)) {
-        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_mark(set, ctx->device);
-    }
-    grid.z = splits;
-    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tw, tx, tx2, part, (int64_t)M, n, M, K, 0, (int64_t)n * M, err);
-    RLB_LAUNCH_CHECK();
-    count_launch(ctx);
-    const int64_t total = (int64_t)n * M;
-    int rg = (int)((total + 255) / 256);
-    if (rg > ctx->sm_count * 8) rg = ctx->sm_count * 8;
-    splitk_reduce_kernel<OT><<<rg, 256, 0, ctx->stream>>>(part, (int64_t)n * M, splits, (int64_t)M, C, ldc, n, M, round_out);
-    RLB_LAUNCH_CHECK();
-    count_launch(ctx);
-    return RLB_OK;
-}
-
-// Grows the context's GEMM scratch (split activations + split-K slabs) to at least `need` bytes.
+// Grows the context's GEMM scratch (split activations + partial tiles) to at least `need` bytes.
 int reserve_scratch(rlb_ctx* ctx, size_t need) {
     if (need <= ctx->gemm_scratch_bytes) return RLB_OK;
     RLB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -360,13 +443,18 @@ template <typename OT, bool TF32>
 int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
               int* err) {
     RLB_TRY(load_encode());
-    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
-    // scratch: [x hi | x lo] for the f32 form, then the split-K slabs (if any)
+    constexpr int BKE = TF32 ? BK / 2 : BK;
+    const int nkb = (K + BKE - 1) / BKE;
+    const long long units = (long long)((n + TM - 1) / TM) * ((M + TN - 1) / TN) * nkb;
+    const int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
+    const Sched sched = make_sched(n, M, nkb, grid);
+    // scratch: [x hi | x lo] for the f32 form, then two partial tiles per CTA (only touched when tiles are dealt out by k-block)
     const size_t xs = TF32 ? (((size_t)n * K * sizeof(float) + 255) & ~(size_t)255) : 0;
-    const int splits = pick_splits(ctx, ((M + BM - 1) / BM) * ((n + bn - 1) / bn), (K + BK - 1) / BK * (TF32 ? 2 : 1));
-    RLB_TRY(reserve_scratch(ctx, 2 * xs + (splits > 1 ? (size_t)splits * n * M * sizeof(float) : 0)));
+    const size_t slabs = sched.rest > 0 ? (size_t)grid * 2 * kSlabFloats * sizeof(float) : 0;
+    RLB_TRY(reserve_scratch(ctx, 2 * xs + slabs));
+    float* part = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + 2 * xs);
     CUtensorMap tw, tx, tx2;
-    RLB_TRY(make_map(&tw, W, M, K, ldw, BM, TF32));
+    RLB_TRY(make_map(&tw, W, M, K, ldw, TN, TF32));
     if (TF32) {
         float* hi = static_cast<float*>(ctx->gemm_scratch);
         float* lo = reinterpret_cast<float*>(static_cast<char*>(ctx->gemm_scratch) + xs);
@@ -376,18 +464,28 @@ int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
         tf32_split_kernel<<<g, 256, 0, ctx->stream>>>(static_cast<const float*>(X), ldx, n, K, hi, lo);
         RLB_LAUNCH_CHECK();
         count_launch(ctx);
-        RLB_TRY(make_map(&tx, hi, n, K, K, bn, true));
-        RLB_TRY(make_map(&tx2, lo, n, K, K, bn, true));
+        RLB_TRY(make_map(&tx, hi, n, K, K, TM, true));
+        RLB_TRY(make_map(&tx2, lo, n, K, K, TM, true));
     } else {
-        RLB_TRY(make_map(&tx, X, n, K, ldx, bn));
+        RLB_TRY(make_map(&tx, X, n, K, ldx, TM));
         tx2 = tx;
     }
-    switch (bn) {
-        case 256: return launch_bn<256, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
-        case 128: return launch_bn<128, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
-        case 64: return launch_bn<64, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
-        default: return launch_bn<32, OT, TF32>(ctx, tw, tx, tx2, C, ldc, n, M, K, round_out, err, 2 * xs);
+    const size_t smem = (size_t)kRingBytes + 1024;
+    auto kern = gemm_tc_kernel<OT, TF32>;
+    static std::atomic<uint64_t> set{0};
+    if (!attr_done(set, ctx->device)) {
+        RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_mark(set, ctx->device);
     }
+    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tx, tx2, tw, C, ldc, n, M, K, round_out, part, err);
+    RLB_LAUNCH_CHECK();
+    count_launch(ctx);
+    if (sched.rest > 0) {
+        gemm_tc_fixup_kernel<OT><<<dim3(sched.rest, TM / 16), 256, 0, ctx->stream>>>(part, C, ldc, n, M, nkb, grid, round_out);
+        RLB_LAUNCH_CHECK();
+        count_launch(ctx);
+    }
+    return RLB_OK;
 }
 
 }  // namespace

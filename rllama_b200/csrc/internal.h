@@ -164,8 +164,13 @@ struct AttnPrefillArgs {
     const void* vcache = nullptr;
     void* out = nullptr;           // [n][heads*hd] weight dtype
     int n = 0, start_pos = 0, heads = 0, hd = 0, max_seq = 0;
+    int* err = nullptr;            // device-visible error word for bounded waits (nullptr: the context's word)
+    bool allow_tc = true;          // the tensor-core kernel may take the call
 };
 int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillArgs& a);
+// Tensor-core form (attention_tc.cu): f16 caches, head_dim 64 / 128, at least 32 query rows.
+bool attn_prefill_tc_supported(rlb_dtype cache_dtype, const AttnPrefillArgs& a);
+int launch_attn_prefill_tc(rlb_ctx* ctx, const AttnPrefillArgs& a, int* err);
 
 // ---------------------------------------------------------------------------------------
 // row-wise / element-wise kernels used by prefill and the tier-1 ops (elementwise.cu)

@@ -31,6 +31,9 @@ struct LayerW {
     void* w2 = nullptr;    // [dim][F_local]
     float* attn_norm = nullptr;
     float* ffn_norm = nullptr;
+    // Layer not resident in HBM (percentage_to_gpu < 1): its five matrices wait here, in pinned host
+    // memory, laid out like the model's HBM staging buffer, which the pointers above then address.
+    char* host = nullptr;
 };
 
 struct ProfSlot {
@@ -60,6 +63,9 @@ struct rlb_model {
     float* rope = nullptr;
     std::vector<LayerW> L;
     std::vector<uint8_t> have;  // [n_layers * 12 + kind] flags
+    int gpu_layers = 0;         // layers 0 .. gpu_layers-1 are resident in HBM (src/transformer.rs:262-274)
+    char* stage = nullptr;      // HBM staging buffer for the matrices of one non-resident layer
+    size_t layer_bytes = 0;     // wqkv | wo | w1 w3 | w2 of one layer
 
     // decode buffers
     float* xa = nullptr;
@@ -188,9 +194,10 @@ int tp_reduce(rlb_model* m, float* part, size_t count, bool decode = true) {
 }
 
 // Decode GEMV: the bulk-copy staged kernel where the shape allows, else the register-staged one.
-int gemv_decode(rlb_model* m, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a) {
+// after_copy: the kernel follows a copy on the stream, not a kernel, so it is launched as an ordinary dependent.
+int gemv_decode(rlb_model* m, rlb_dtype dtype, int prologue, int epilogue, const GemvArgs& a, bool after_copy = false) {
     if (m->use_stream) {
-        const int s = launch_gemv_stream(m->ctx, dtype, prologue, epilogue, a, m->scalars + 8, m->use_pdl && !m->profile);
+        const int s = launch_gemv_stream(m->ctx, dtype, prologue, epilogue, a, m->scalars + 8, m->use_pdl && !m->profile && !after_copy);
         if (s != RLB_ERR_STATE) return s;
     }
     if (a.ll_inbox != nullptr || a.n_outs > 0)
@@ -233,6 +240,8 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         const LayerW& W = m->L[l];
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
         char* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
+        if (W.host)  // not resident: bring the layer's matrices into the staging buffer (stream order keeps the previous layer's reads ahead of it)
+            RLB_CUDA(cudaMemcpyAsync(m->stage, W.host, m->layer_bytes, cudaMemcpyHostToDevice, ctx->stream));
         {   // 1. norm + q/k/v projection + RoPE + cache append
             GemvArgs a;
             a.W = W.wqkv; a.rows = 3 * m->nq; a.K = d; a.ldw = d;
@@ -245,7 +254,7 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
             a.qbuf = m->qbuf; a.kcache = kc; a.vcache = vc; a.rope = m->rope; a.pos_ptr = pos;
             a.nq = m->nq; a.hd = m->hd; a.max_seq = m->p.max_seq_len;
             prof_mark(m, PC_QKV);
-            RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_QKV, a));
+            RLB_TRY(gemv_decode(m, m->wdt, PRO_NORM, EPI_QKV, a, W.host != nullptr));
         }
         {   // 2. attention
             AttnDecodeArgs a;
@@ -401,6 +410,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         const LayerW& W = m->L[l];
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
         char* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
+        if (W.host) RLB_CUDA(cudaMemcpyAsync(m->stage, W.host, m->layer_bytes, cudaMemcpyHostToDevice, ctx->stream));
         RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.attn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         // q, k and v in one GEMM: row i of the result is [q_i | k_i | v_i]
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.wqkv, d, m->pf_qkv, 3 * nq, n, 3 * nq, d, f16, m->scalars + 8, m->w_f16_exact));
@@ -408,7 +418,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
                                    m->p.max_seq_len, m->rope, m->wdt, kc, vc));
         AttnPrefillArgs aa;
         aa.q = m->pf_qkv; aa.q_ld = 3 * nq; aa.kcache = kc; aa.vcache = vc; aa.out = m->pf_o; aa.n = n; aa.start_pos = start_pos;
-        aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len;
+        aa.heads = m->nh; aa.hd = m->hd; aa.max_seq = m->p.max_seq_len; aa.err = m->scalars + 8;
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
@@ -433,7 +443,7 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
 
 // The decode kernels raise scalars[8] when a bounded wait ran out; h points at its host copy.
 int check_device_flag(const int32_t* h) {
-    if (*h == 3) return rlb_fail(RLB_ERR_CUDA, "the prefill GEMM gave up waiting on a shared-memory barrier (results are invalid)");
+    if (*h == 3) return rlb_fail(RLB_ERR_CUDA, "a prefill kernel (GEMM or attention) gave up waiting on a shared-memory barrier (results are invalid)");
     if (*h == 2) return rlb_fail(RLB_ERR_COMM, "a decode kernel gave up waiting for another rank's partial sums (results are invalid)");
     if (*h != 0) return rlb_fail(RLB_ERR_CUDA, "a decode kernel gave up waiting on a shared-memory barrier (results are invalid)");
     return RLB_OK;
@@ -508,12 +518,29 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
     A((void**)&m->norm, d * 4);
     A((void**)&m->output, (size_t)m->V * d * 4);
     A((void**)&m->rope, (size_t)p->max_seq_len * (hd / 2) * 2 * 4);
-    for (auto& W : m->L) {
-        A(&W.wqkv, (size_t)3 * m->nq * d * m->wsz);
-        A(&W.wo, d * m->nq * m->wsz);
-        A(&W.w1, (size_t)2 * m->F * d * m->wsz);  // w1 and w3 back to back: one GEMM serves both at prefill
+    // DataSettings::percentage_to_gpu (src/transformer.rs:91-103) and the rule of :262-274, in f32 as there
+    float pct = p->has_percentage_to_gpu ? p->percentage_to_gpu : 1.0f;
+    if (pct >= 1.0f) pct = 1.0f;
+    if (pct < 0.0f) pct = 0.0f;
+    if (pct != pct) pct = 0.0f;
+    m->gpu_layers = std::min(p->n_layers, (int)roundf(pct * (float)(p->n_layers - 1)) + 1);
+    const size_t b_qkv = (size_t)3 * m->nq * d * m->wsz, b_wo = d * m->nq * m->wsz, b_w13 = (size_t)2 * m->F * d * m->wsz,
+                 b_w2 = d * m->F * m->wsz;
+    m->layer_bytes = b_qkv + b_wo + b_w13 + b_w2;
+    if (m->gpu_layers < p->n_layers) A((void**)&m->stage, m->layer_bytes);
+    for (int l = 0; l < p->n_layers; l++) {
+        LayerW& W = m->L[l];
+        if (l < m->gpu_layers) {
+            A(&W.wqkv, b_qkv);
+            A(&W.wo, b_wo);
+            A(&W.w1, b_w13);  // w1 and w3 back to back: one GEMM serves both at prefill
+            A(&W.w2, b_w2);
+        } else if (s == RLB_OK) {
+            cudaError_t e = cudaHostAlloc((void**)&W.host, m->layer_bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+            if (e != cudaSuccess) s = rlb_fail(RLB_ERR_OOM, "pinned host memory for layer %d (%zu bytes): %s", l, m->layer_bytes, cudaGetErrorString(e));
+            W.wqkv = m->stage; W.wo = m->stage + b_qkv; W.w1 = m->stage + b_qkv + b_wo; W.w2 = m->stage + b_qkv + b_wo + b_w13;
+        }
         if (W.w1) W.w3 = (char*)W.w1 + (size_t)m->F * d * m->wsz;
-        A(&W.w2, d * m->F * m->wsz);
         A((void**)&W.attn_norm, d * 4);
         A((void**)&W.ffn_norm, d * 4);
     }
@@ -600,6 +627,8 @@ int rlb_model_set_tensor(rlb_model* m, rlb_tensor_kind kind, int32_t layer, cons
         case RLB_W2: er = d; ec = F; nr = d; c0 = m->f0; nc = m->F; dst = W->w2; dst_ld = m->F; break;
         default: return rlb_fail(RLB_ERR_INVALID, "unknown tensor kind %d", (int)kind);
     }
+    // a matrix of a layer that is not resident in HBM goes to its place in the layer's pinned host block
+    if (W && W->host && kind >= RLB_WQ && kind <= RLB_W3) dst = W->host + ((char*)dst - m->stage);
     // 1-D gains may arrive as [1][dim] or [dim][1]-like flat rows
     if (er == 1 && rows * cols == d) { rows = 1; cols = d; if (capacity_cols < d) capacity_cols = d; }
     if (rows != er || cols != ec)
@@ -667,9 +696,14 @@ int rlb_model_free(rlb_model* m) {
                     m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g3, m->pf_g, m->pf_last};
     for (void* p : ptrs) if (p) cudaFree(p);
     for (auto& W : m->L) {
+        if (W.host) {  // the matrix pointers address the shared staging buffer
+            cudaFreeHost(W.host);
+            W.wqkv = W.wo = W.w1 = W.w2 = nullptr;
+        }
         void* lp[] = {W.wqkv, W.wo, W.w1, W.w2, W.attn_norm, W.ffn_norm};
         for (void* p : lp) if (p) cudaFree(p);
     }
+    if (m->stage) cudaFree(m->stage);
     if (m->h_scalars) cudaFreeHost(m->h_scalars);
     if (m->h_logits) cudaFreeHost(m->h_logits);
     if (m->h_tokens) cudaFreeHost(m->h_tokens);
@@ -915,6 +949,7 @@ int rlb_model_get_stat(rlb_model* m, const char* name, double* value) {
     if (!strcmp(name, "attn_split")) { *value = m->n_split; return RLB_OK; }
     if (!strcmp(name, "prof_steps")) { *value = m->prof_steps; return RLB_OK; }
     if (!strcmp(name, "local_heads")) { *value = m->nh; return RLB_OK; }
+    if (!strcmp(name, "layers_on_gpu")) { *value = m->gpu_layers; return RLB_OK; }
     if (!strcmp(name, "first_head")) { *value = m->head0; return RLB_OK; }
     if (!strcmp(name, "local_ffn")) { *value = m->F; return RLB_OK; }
     if (!strcmp(name, "local_vocab")) { *value = m->V; return RLB_OK; }

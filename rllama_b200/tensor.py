@@ -99,6 +99,10 @@ class CudaTensor:
         """self <- single-query attention of q over positions 0..pos of the caches."""
         check(_ffi.lib().rlb_attention_decode(self._h, q._h, kcache._h, vcache._h, heads, max_seq_len, pos, n_split))
 
+    def attention_prefill(self, q, kcache, vcache, heads, max_seq_len, start_pos=0, tensor_cores=True):
+        """self <- causal attention of the rows of q (row i attends to positions 0..start_pos+i)."""
+        check(_ffi.lib().rlb_attention_prefill(self._h, q._h, kcache._h, vcache._h, heads, max_seq_len, start_pos, int(bool(tensor_cores))))
+
     def attention_decode_static(self, q, kcache, vcache, heads, max_seq_len, pos, n_split=1):
         """Same as ``attention_decode`` but allocation-free: the kernel's scratch is a fixed
         array inside the library (for hosts that cannot allocate on the token path). Fails

@@ -15,8 +15,9 @@ from .tensor import Cuda
 
 
 class DataSettings:
-    """``DataSettings`` (``src/transformer.rs:38-109``). ``percentage_to_gpu`` is kept for
-    surface compatibility; this backend has no CPU path, so every layer is on the GPU."""
+    """``DataSettings`` (``src/transformer.rs:38-109``). ``percentage_to_gpu``: layer ``i`` is resident in
+    HBM iff ``i <= round(p * (n_layers - 1))``; this backend has no CPU path, so the matrices of the other
+    layers wait in pinned host memory and are copied into an HBM staging buffer inside every forward call."""
 
     def __init__(self, cl=None):
         self.cl = cl
@@ -33,6 +34,11 @@ class DataSettings:
             p = 0.0
         self._percentage_to_gpu = min(1.0, max(0.0, p))
         return self
+
+    def layers_on_gpu(self, n_layers):
+        """Number of layers resident in HBM (src/transformer.rs:262-274; f32 arithmetic, round half away from zero)."""
+        x = float(np.float32(self._percentage_to_gpu) * np.float32(n_layers - 1))
+        return min(n_layers, int(np.floor(x + 0.5)) + 1)
 
 
 class Transformer:
@@ -52,7 +58,7 @@ class Transformer:
         self.force_f16 = ds._force_f16
         self.tp_rank, self.tp_size = tp_rank, tp_size
         p = ModelParams(dim, n_layers, n_heads, ffn_dim, vocab_size, max_seq_len, float(eps), int(ds._force_f16),
-                        int(tp_rank), int(tp_size))
+                        int(tp_rank), int(tp_size), 1, float(ds._percentage_to_gpu))
         self._h = ctypes.c_void_p()
         check(_ffi.lib().rlb_model_create(self.cl._h, ctypes.byref(p), ctypes.byref(self._h)))
 
@@ -65,7 +71,8 @@ class Transformer:
         self = cls.__new__(cls)
         ds = data_settings or DataSettings()
         self.cl = ds.cl or Cuda(verbose=False, nth_device=0)
-        p = ModelParams(dim, n_layers, n_heads, 0, 0, max_seq_len, float(eps), int(ds._force_f16), int(tp_rank), int(tp_size))
+        p = ModelParams(dim, n_layers, n_heads, 0, 0, max_seq_len, float(eps), int(ds._force_f16), int(tp_rank), int(tp_size),
+                        1, float(ds._percentage_to_gpu))
         self._h = ctypes.c_void_p()
         check(_ffi.lib().rlb_model_from_llama_source(self.cl._h, data_source._h, ctypes.byref(p), ctypes.byref(self._h)))
         self.dim, self.n_layers, self.n_heads = dim, n_layers, n_heads

@@ -250,6 +250,41 @@ def test_cache_contents_clone_and_shift(cuda_ctx):
     assert np.array_equal(gc.read("v", 0, 2, 15), before[15]) and np.array_equal(gc.read("v", 0, 2, 14), before[15])
 
 
+@pytest.mark.parametrize("f16", [False, True])
+def test_percentage_to_gpu_gives_identical_logits(cuda_ctx, f16):
+    """--percentage-to-gpu (src/transformer.rs:91-103, :262-274): layers beyond round(p * (L - 1)) are not
+    resident in HBM; their matrices are copied in from pinned host memory inside every call and the same
+    kernels run, so the logits are bit-identical to the all-resident model."""
+    from rllama_b200 import DataSettings, Transformer
+    cfg = cfg_variant("tiny", n_layers=8, vocab=2000, max_seq_len=64)
+    prompt = S.synth_tokens(40, cfg["vocab"])
+    runs = {}
+    for p in (1.0, 0.5, 0.0, float("nan")):
+        ds = DataSettings(cl=cuda_ctx).percentage_to_gpu(p)
+        if f16:
+            ds = ds.force_f16()
+        m = Transformer(cfg["dim"], cfg["n_layers"], cfg["n_heads"], cfg["ffn"], cfg["vocab"], cfg["max_seq_len"], cfg["norm_eps"], ds)
+        S.load_into(m, cfg)
+        m.finalize()
+        assert int(m.get_stat("layers_on_gpu")) == ds.layers_on_gpu(cfg["n_layers"])
+        c = m.make_caches()
+        out = [m.forward(prompt, 0, c)]
+        for i in range(3):
+            out.append(m.forward([int(np.argmax(out[-1]))], len(prompt) + i, c))
+        c2 = m.make_caches()
+        first = m.forward_greedy(prompt, 0, c2)
+        toks, _ = m.decode_greedy(first, len(prompt), 6, c2)   # graph replays with the copies inside
+        runs[repr(p)] = (np.stack(out), toks)
+        m.free()
+    assert DataSettings().percentage_to_gpu(0.5).layers_on_gpu(8) == 5   # round(3.5) = 4 -> layers 0..4
+    assert DataSettings().percentage_to_gpu(0.0).layers_on_gpu(8) == 1 and DataSettings().percentage_to_gpu(float("nan")).layers_on_gpu(8) == 1
+    assert DataSettings().percentage_to_gpu(7.0).layers_on_gpu(8) == 8
+    ref_logits, ref_toks = runs[repr(1.0)]
+    for key, (logits, toks) in runs.items():
+        assert np.array_equal(logits, ref_logits), key
+        assert np.array_equal(toks, ref_toks), key
+
+
 def test_construction_errors(cuda_ctx):
     from rllama_b200 import DataSettings, Transformer
     cfg = cfg_variant("tiny", n_layers=1, vocab=1000)

@@ -150,3 +150,67 @@ def test_attention_decode_op(cuda_ctx, dtype):
     with pytest.raises(RllamaError):
         bad = cuda_ctx.zeros(1, 8, F32)
         bad.attention_decode(bad, bad, bad, 1, 4, 9, 1)
+
+
+def prefill_reference(q, k, v, heads, hd, max_seq, start_pos):
+    """float64 causal attention: row i over positions 0..start_pos+i (rllama src/transformer.rs:727-781,
+    mask src/tensor.rs:496-508)."""
+    n = q.shape[0]
+    out = np.zeros((n, heads * hd))
+    for h in range(heads):
+        K = k[h * max_seq:(h + 1) * max_seq].astype(np.float64)
+        V = v[h * max_seq:(h + 1) * max_seq].astype(np.float64)
+        s = q[:, h * hd:(h + 1) * hd].astype(np.float64) @ K.T / np.sqrt(hd)
+        for i in range(n):
+            t = start_pos + i + 1
+            p = np.exp(s[i, :t] - s[i, :t].max())
+            out[i, h * hd:(h + 1) * hd] = (p / p.sum()) @ V[:t]
+    return out
+
+
+@pytest.mark.parametrize("heads,hd,max_seq,start_pos,n", [(3, 128, 512, 0, 300), (2, 64, 700, 0, 650), (2, 128, 400, 37, 200),
+                                                          (5, 64, 160, 100, 33), (1, 128, 2048, 0, 1792)])
+def test_attention_prefill_on_tensor_cores(cuda_ctx, heads, hd, max_seq, start_pos, n):
+    """The tensor-core kernel (f16 cache, q and the softmax weights as two f16 halves each) against float64 and
+    against the CUDA-core kernel: partial last query block, several cache tiles, the diagonal tiles' mask, a
+    chunk at start_pos > 0, cache rows beyond the attended prefix holding other data."""
+    rng = np.random.default_rng(7)
+    q = rng.normal(0, 1.3, (n, heads * hd)).astype(np.float32)
+    k = rng.normal(0, 1.0, (heads * max_seq, hd)).astype(np.float16)
+    v = rng.normal(0, 1.0, (heads * max_seq, hd)).astype(np.float16)
+    tq, tk, tv = cuda_ctx.upload(q), cuda_ctx.upload(k), cuda_ctx.upload(v)
+    tc, cc = cuda_ctx.zeros(n, heads * hd, F16), cuda_ctx.zeros(n, heads * hd, F16)
+    tc.attention_prefill(tq, tk, tv, heads, max_seq, start_pos, tensor_cores=True)
+    cc.attention_prefill(tq, tk, tv, heads, max_seq, start_pos, tensor_cores=False)
+    got, other = tc.to_numpy().astype(np.float64), cc.to_numpy().astype(np.float64)
+    want = prefill_reference(q, k, v, heads, hd, max_seq, start_pos)
+    # both kernels round an f32 result to f16 once: half an f16 ulp of values up to ~4, plus summation-order noise
+    assert np.abs(got - want).max() <= 2e-3
+    assert np.abs(other - want).max() <= 2e-3
+    # the two kernels agree except where f32 noise flips the f16 rounding
+    assert (got != other).mean() < 0.02
+    for t in (tq, tk, tv, tc, cc):
+        t.free()
+
+
+def test_attention_prefill_split_precision(cuda_ctx):
+    """An f32 output would show the precision of the two-half split; through the f16 output it shows as
+    agreement of the rounded results: values chosen so that the softmax is sharp (large scores) and flat
+    (tiny scores) in different heads."""
+    rng = np.random.default_rng(8)
+    heads, hd, max_seq, n = 2, 128, 256, 256
+    q = rng.normal(0, 1.0, (n, heads * hd)).astype(np.float32)
+    q[:, :hd] *= 6.0      # head 0: sharp softmax
+    q[:, hd:] *= 0.01     # head 1: nearly uniform weights
+    k = rng.normal(0, 1.0, (heads * max_seq, hd)).astype(np.float16)
+    v = rng.normal(0, 1.0, (heads * max_seq, hd)).astype(np.float16)
+    tq, tk, tv = cuda_ctx.upload(q), cuda_ctx.upload(k), cuda_ctx.upload(v)
+    tc = cuda_ctx.zeros(n, heads * hd, F16)
+    tc.attention_prefill(tq, tk, tv, heads, max_seq, 0)
+    got = tc.to_numpy().astype(np.float64)
+    want = prefill_reference(q, k, v, heads, hd, max_seq, 0)
+    ulp = np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
+    assert (np.abs(got - want) <= 0.51 * ulp + 1e-6).mean() > 0.99  # correctly rounded almost everywhere (a lost low half would flip ~10 %)
+    assert np.abs(got - want).max() <= 2e-3
+    for t in (tq, tk, tv, tc):
+        t.free()

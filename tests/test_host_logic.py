@@ -63,6 +63,9 @@ def test_data_settings_clamps_percentage():
     ds = DataSettings().percentage_to_gpu(float("nan"))
     assert ds._percentage_to_gpu == 0.0
     assert DataSettings().percentage_to_gpu(7)._percentage_to_gpu == 1.0
+    # layer i is resident iff i <= round(p * (L - 1)) (src/transformer.rs:262-274)
+    assert [DataSettings().percentage_to_gpu(p).layers_on_gpu(32) for p in (0.0, 0.01, 0.5, 0.99, 1.0)] == [1, 1, 17, 32, 32]
+    assert DataSettings().percentage_to_gpu(0.5).layers_on_gpu(8) == 5 and DataSettings().percentage_to_gpu(0.5).layers_on_gpu(1) == 1
     assert DataSettings().force_f16()._force_f16
 
 
