@@ -186,6 +186,7 @@ int rlb_model_set_tensor(rlb_model* m, rlb_tensor_kind kind, int32_t layer, cons
                          int64_t rows, int64_t cols, int64_t capacity_cols, rlb_dtype dtype);
 /* Checks that every tensor was given, builds the RoPE table (src/transformer.rs:858-885). */
 int rlb_model_finalize(rlb_model* m);
+/* Frees the model. Its caches (rlb_caches_*) refer to it: free them first.                */
 int rlb_model_free(rlb_model* m);
 
 /* Tensor-parallel wiring, one process per GPU. Either
@@ -200,6 +201,11 @@ int rlb_tp_nccl_unique_id(void* id128);
 int rlb_tp_nccl_init(rlb_model* m, const void* id128);
 int rlb_tp_peer_export(rlb_model* m, void* handle128);
 int rlb_tp_peer_import(rlb_model* m, const void* handles, int32_t n_handles);
+/* (b) for ranks that live in ONE process (one host thread or several, one context per GPU): the
+ * models of all ranks, indexed by rank (the entry of m's own rank may be m or NULL). Exchange
+ * buffers are allocated as needed and peer access between the devices is enabled. No counterpart
+ * in the reference.                                                                       */
+int rlb_tp_peer_import_local(rlb_model* m, rlb_model* const* peers, int32_t n_peers);
 /* mode: 0 = NCCL all-reduce / all-gather, 1 = fused push exchange over peer memory (needs
  * rlb_tp_peer_import; prefill keeps using NCCL). Every rank must switch at the same step. */
 int rlb_tp_set_mode(rlb_model* m, int32_t mode);

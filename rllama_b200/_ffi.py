@@ -20,7 +20,7 @@ EXPORTS = [
     "rlb_copy_inplace", "rlb_transpose_from", "rlb_hadamard_product_inplace", "rlb_silu_inplace",
     "rlb_matrix_mul_inplace_transposed", "rlb_attention_decode", "rlb_attention_decode_static", "rlb_attention_prefill",
     "rlb_model_create", "rlb_model_set_tensor", "rlb_model_finalize", "rlb_model_free",
-    "rlb_tp_nccl_unique_id", "rlb_tp_nccl_init", "rlb_tp_peer_export", "rlb_tp_peer_import", "rlb_tp_set_mode",
+    "rlb_tp_nccl_unique_id", "rlb_tp_nccl_init", "rlb_tp_peer_export", "rlb_tp_peer_import", "rlb_tp_peer_import_local", "rlb_tp_set_mode",
     "rlb_caches_create", "rlb_caches_true_clone", "rlb_caches_shift_left", "rlb_caches_free", "rlb_caches_read",
     "rlb_forward", "rlb_forward_greedy", "rlb_decode_greedy",
     "rlb_model_set_option", "rlb_model_get_stat",
@@ -84,7 +84,7 @@ def lib():
         "rlb_model_set_tensor": [vp, ci, i32, vp, i64, i64, i64, ci],
         "rlb_model_finalize": [vp], "rlb_model_free": [vp],
         "rlb_tp_nccl_unique_id": [vp], "rlb_tp_nccl_init": [vp, vp],
-        "rlb_tp_peer_export": [vp, vp], "rlb_tp_peer_import": [vp, vp, i32], "rlb_tp_set_mode": [vp, i32],
+        "rlb_tp_peer_export": [vp, vp], "rlb_tp_peer_import": [vp, vp, i32], "rlb_tp_peer_import_local": [vp, vp, i32], "rlb_tp_set_mode": [vp, i32],
         "rlb_caches_create": [vp, P(vp)], "rlb_caches_true_clone": [vp, P(vp)], "rlb_caches_shift_left": [vp, i32],
         "rlb_caches_free": [vp], "rlb_caches_read": [vp, i32, i32, i32, i32, vp],
         "rlb_forward": [vp, vp, vp, i32, i32, vp],

@@ -28,6 +28,7 @@
 #include <condition_variable>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <optional>
 #include <string>
@@ -313,33 +314,31 @@ inline bool parse_request(const std::string& body, InferenceRequest* req) {
 // ---------------------------------------------------------------------------------------------
 // AttentionCacheRepository (src/rllama_main.rs:570-619): token sequence -> (caches, position, time)
 // ---------------------------------------------------------------------------------------------
+// Entries hold counted references to the device caches. A KV cache is append-only and an entry's position says
+// how many of its rows are valid, so the entries a generating session leaves behind token after token can all
+// refer to the ONE physical cache that session keeps writing to: rows below an entry's position never change.
+using CachesRef = std::shared_ptr<rlb_caches>;
+inline CachesRef make_caches_ref(rlb_caches* c) { return CachesRef(c, [](rlb_caches* p) { rlb_caches_free(p); }); }
+
 class CacheRepository {
 public:
     explicit CacheRepository(size_t max_size) : max_(max_size) {}
-    ~CacheRepository() { for (auto& kv : map_) rlb_caches_free(kv.second.caches); }
-    // If the sequence is known: a clone of its caches and their position.
-    bool get_clone(const std::vector<int32_t>& tokens, rlb_caches** clone, size_t* pos) {
+    // If the sequence is known: the caches of its entry and their position.
+    bool get(const std::vector<int32_t>& tokens, CachesRef* caches, size_t* pos) const {
         auto it = map_.find(tokens);
         if (it == map_.end()) return false;
+        *caches = it->second.caches;
         *pos = it->second.pos;
-        *clone = nullptr;
-        if (rlb_caches_true_clone(it->second.caches, clone) != RLB_OK) *clone = nullptr;
         return true;
     }
-    // Takes ownership of `caches`.
-    void put(const std::vector<int32_t>& tokens, rlb_caches* caches, size_t pos) {
-        auto it = map_.find(tokens);
-        if (it != map_.end()) {
-            rlb_caches_free(it->second.caches);
-            map_.erase(it);
-        }
-        map_[tokens] = Entry{caches, pos, std::chrono::steady_clock::now()};
+    void put(const std::vector<int32_t>& tokens, CachesRef caches, size_t pos) {
+        map_[tokens] = Entry{std::move(caches), pos, std::chrono::steady_clock::now()};
         limit_size();
     }
     size_t size() const { return map_.size(); }
 
 private:
-    struct Entry { rlb_caches* caches; size_t pos; std::chrono::steady_clock::time_point t; };
+    struct Entry { CachesRef caches; size_t pos; std::chrono::steady_clock::time_point t; };
     std::map<std::vector<int32_t>, Entry> map_;
     size_t max_;
     void limit_size() {
@@ -347,7 +346,6 @@ private:
             auto oldest = map_.begin();
             for (auto it = map_.begin(); it != map_.end(); ++it)
                 if (it->second.t < oldest->second.t) oldest = it;
-            rlb_caches_free(oldest->second.caches);
             map_.erase(oldest);
         }
     }
@@ -387,36 +385,45 @@ public:
     // False when the stream has ended.
     bool next_line(std::string* line) {
         if (tokens_.size() >= req_max_seq_len_ || new_tokens_ >= req_max_new_tokens_) return false;
-        rlb_caches* caches = nullptr;
+        CachesRef caches;
         size_t update_pos = 0;
         {
             std::lock_guard<std::mutex> g(st_->repo_mu);
-            rlb_caches* clone = nullptr;
+            CachesRef found;
             size_t pos = 0;
-            if (st_->repo.get_clone(tokens_, &clone, &pos)) {
-                if (pos >= prev_pos_ && clone != nullptr) {
-                    caches = clone;
+            auto fresh = [&]() { rlb_caches* c = nullptr; ok(rlb_caches_create(st_->model, &c)); return make_caches_ref(c); };
+            if (st_->repo.get(tokens_, &found, &pos)) {
+                if (pos >= prev_pos_) {
+                    if (found == own_) {
+                        // The entry this session stored after its previous token refers to the caches it is
+                        // generating into: they are used in place (the reference clones here,
+                        // src/rllama_main.rs:489-503): no allocation, no copy of the whole cache, and the
+                        // caches' decode graph is replayed.
+                        caches = found;
+                    } else {  // somebody else's entry: a true clone, as in the reference
+                        rlb_caches* clone = nullptr;
+                        ok(rlb_caches_true_clone(found.get(), &clone));
+                        caches = make_caches_ref(clone);
+                    }
                     update_pos = pos;
                 } else {
-                    if (clone) rlb_caches_free(clone);
-                    ok(rlb_caches_create(st_->model, &caches));
+                    caches = fresh();
                     // The reference continues from prev_pos with these empty caches; positions
                     // before prev_pos would then be attended as zeros, so the sequence is run again
                     // from the start instead.
                     prev_pos_ = 0;
                 }
             } else {
-                ok(rlb_caches_create(st_->model, &caches));
+                caches = fresh();
                 rlb_caches* keep = nullptr;
-                ok(rlb_caches_true_clone(caches, &keep));
-                st_->repo.put(tokens_, keep, prev_pos_);
+                ok(rlb_caches_true_clone(caches.get(), &keep));
+                st_->repo.put(tokens_, make_caches_ref(keep), prev_pos_);
                 update_pos = prev_pos_;
             }
         }
         if (update_pos > prev_pos_) prev_pos_ = update_pos;
-        const int st = rlb_forward(st_->model, caches, tokens_.data() + prev_pos_, (int32_t)(tokens_.size() - prev_pos_), (int32_t)prev_pos_,
-                                   logits_.data());
-        if (st != RLB_OK) { rlb_caches_free(caches); ok(st); }
+        ok(rlb_forward(st_->model, caches.get(), tokens_.data() + prev_pos_, (int32_t)(tokens_.size() - prev_pos_), (int32_t)prev_pos_,
+                       logits_.data()));
         prev_pos_ = tokens_.size();
         int32_t tok = 0;
         float prob = 0.f;
@@ -425,6 +432,7 @@ public:
         {
             std::lock_guard<std::mutex> g(st_->repo_mu);
             st_->repo.put(tokens_, caches, prev_pos_);
+            own_ = caches;
         }
         new_tokens_++;
         const char* piece = nullptr;
@@ -468,6 +476,7 @@ private:
     std::vector<int32_t> tokens_;
     std::vector<float> logits_;
     size_t req_max_seq_len_, req_max_new_tokens_, new_tokens_ = 0, prev_pos_ = 0;
+    CachesRef own_;  // the caches this session generates into (also referenced by the entries it stored)
     bool no_token_sampling_, stop_at_end_token_;
 };
 

@@ -25,13 +25,77 @@ __global__ void embed_kernel(const float* __restrict__ table, const int32_t* __r
     for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) dst[i] = src[i];
 }
 
-// RMSNorm::forward (src/transformer.rs:476-480), one CTA per row.
+// RMSNorm::forward (src/transformer.rs:476-480), one CTA per row, optionally after the residual add of
+// TransformerBlock::forward (src/transformer.rs:442-445): x += round?(y), then out = cast(norm(x) * gain).
+// The row (up to 8192 elements) stays in registers between the two passes; every load is issued before use.
 template <typename OT>
-__global__ void rmsnorm_rows_kernel(const float* __restrict__ x, int dim, const float* __restrict__ gain, float eps, OT* __restrict__ out) {
-    __shared__ float red[32];
-    const float* xr = x + (int64_t)blockIdx.x * dim;
+__global__ void __launch_bounds__(256) add_norm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int do_round, int dim,
+                                                            const float* __restrict__ gain, float eps, OT* __restrict__ out) {
+    constexpr int G = 8;  // float4 groups per thread: 8 * 4 * 256 = 8192 elements
+    __shared__ float red[8];
+    float* xr = x + (int64_t)blockIdx.x * dim;
+    const float* yr = y ? y + (int64_t)blockIdx.x * dim : nullptr;
+    float4 v[G], w[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const int i = (g * 256 + threadIdx.x) * 4;
+        if (i < dim) {
+            v[g] = *reinterpret_cast<const float4*>(xr + i);
+            if (yr) w[g] = *reinterpret_cast<const float4*>(yr + i);
+        }
+    }
     float ss = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const int i = (g * 256 + threadIdx.x) * 4;
+        if (i < dim) {
+            if (yr) {
+                float4 t = w[g];
+                if (do_round) { t.x = round_f16(t.x); t.y = round_f16(t.y); t.z = round_f16(t.z); t.w = round_f16(t.w); }
+                v[g].x += t.x; v[g].y += t.y; v[g].z += t.z; v[g].w += t.w;
+                *reinterpret_cast<float4*>(xr + i) = v[g];
+            }
+            ss = fmaf(v[g].x, v[g].x, ss); ss = fmaf(v[g].y, v[g].y, ss); ss = fmaf(v[g].z, v[g].z, ss); ss = fmaf(v[g].w, v[g].w, ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; wi++) tot += red[wi];
+    const float scale = 1.0f / sqrtf(tot / (float)dim + eps);
+    OT* o = out + (int64_t)blockIdx.x * dim;
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const int i = (g * 256 + threadIdx.x) * 4;
+        if (i < dim) {
+            const float4 gn = *reinterpret_cast<const float4*>(gain + i);
+            o[i] = cast_to<OT>(__fmul_rn(__fmul_rn(v[g].x, scale), gn.x));
+            o[i + 1] = cast_to<OT>(__fmul_rn(__fmul_rn(v[g].y, scale), gn.y));
+            o[i + 2] = cast_to<OT>(__fmul_rn(__fmul_rn(v[g].z, scale), gn.z));
+            o[i + 3] = cast_to<OT>(__fmul_rn(__fmul_rn(v[g].w, scale), gn.w));
+        }
+    }
+}
+
+// The same for rows the register form does not take (more than 8192 elements, or a width that is not a multiple of 4).
+template <typename OT>
+__global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int do_round, int dim, const float* __restrict__ gain,
+                                    float eps, OT* __restrict__ out) {
+    __shared__ float red[32];
+    float* xr = x + (int64_t)blockIdx.x * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = xr[i];
+        if (y) {
+            const float t = y[(int64_t)blockIdx.x * dim + i];
+            v += do_round ? round_f16(t) : t;
+            xr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -43,31 +107,50 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, int dim, const 
     for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = cast_to<OT>(__fmul_rn(__fmul_rn(xr[i], scale), gain[i]));
 }
 
-// apply_rotary_emb (src/transformer.rs:823-856) + the cache write loop (:751-761).
+// apply_rotary_emb (src/transformer.rs:823-856) + the cache write loop (:751-761). grid (tokens, ceil(heads / 8)):
+// a warp per (token, head); a lane handles two (re, im) pairs (one float4 of q, k and v) per step.
 template <typename CT>
-__global__ void rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int64_t ld,
-                                   int start_pos, int heads, int hd, int max_seq, const float* __restrict__ rope,
-                                   CT* __restrict__ kcache, CT* __restrict__ vcache) {
-    const int i = blockIdx.x, pos = start_pos + i, nq = heads * hd;
-    for (int p = threadIdx.x; p < nq / 2; p += blockDim.x) {
-        const int head = (2 * p) / hd, c = 2 * p - head * hd;
-        const float fr = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2], fi = rope[((int64_t)pos * (hd / 2) + (c >> 1)) * 2 + 1];
-        const int64_t idx = (int64_t)i * ld + 2 * p;
-        const float qr = q[idx], qi = q[idx + 1], kr = k[idx], ki = k[idx + 1];
-        q[idx] = __fsub_rn(__fmul_rn(qr, fr), __fmul_rn(qi, fi));
-        q[idx + 1] = __fadd_rn(__fmul_rn(qr, fi), __fmul_rn(qi, fr));
+__global__ void __launch_bounds__(256) rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int64_t ld,
+                                                          int start_pos, int heads, int hd, int max_seq, const float* __restrict__ rope,
+                                                          CT* __restrict__ kcache, CT* __restrict__ vcache) {
+    const int i = blockIdx.x, pos = start_pos + i;
+    const int head = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (head >= heads) return;
+    for (int c = lane * 4; c < hd; c += 128) {
+        const int64_t idx = (int64_t)i * ld + head * hd + c;
+        const float4 qv = *reinterpret_cast<const float4*>(q + idx), kv = *reinterpret_cast<const float4*>(k + idx);
+        const float4 vv = *reinterpret_cast<const float4*>(v + idx);
+        const float4 f = *reinterpret_cast<const float4*>(rope + ((int64_t)pos * (hd / 2) + (c >> 1)) * 2);  // (cos, sin) of two pairs
+        float4 qo, ko;
+        qo.x = __fsub_rn(__fmul_rn(qv.x, f.x), __fmul_rn(qv.y, f.y)); qo.y = __fadd_rn(__fmul_rn(qv.x, f.y), __fmul_rn(qv.y, f.x));
+        qo.z = __fsub_rn(__fmul_rn(qv.z, f.z), __fmul_rn(qv.w, f.w)); qo.w = __fadd_rn(__fmul_rn(qv.z, f.w), __fmul_rn(qv.w, f.z));
+        ko.x = __fsub_rn(__fmul_rn(kv.x, f.x), __fmul_rn(kv.y, f.y)); ko.y = __fadd_rn(__fmul_rn(kv.x, f.y), __fmul_rn(kv.y, f.x));
+        ko.z = __fsub_rn(__fmul_rn(kv.z, f.z), __fmul_rn(kv.w, f.w)); ko.w = __fadd_rn(__fmul_rn(kv.z, f.w), __fmul_rn(kv.w, f.z));
+        *reinterpret_cast<float4*>(q + idx) = qo;
         const int64_t cidx = ((int64_t)head * max_seq + pos) * hd + c;
-        kcache[cidx] = cast_to<CT>(__fsub_rn(__fmul_rn(kr, fr), __fmul_rn(ki, fi)));
-        kcache[cidx + 1] = cast_to<CT>(__fadd_rn(__fmul_rn(kr, fi), __fmul_rn(ki, fr)));
-        vcache[cidx] = cast_to<CT>(v[idx]);
-        vcache[cidx + 1] = cast_to<CT>(v[idx + 1]);
+        kcache[cidx] = cast_to<CT>(ko.x); kcache[cidx + 1] = cast_to<CT>(ko.y); kcache[cidx + 2] = cast_to<CT>(ko.z); kcache[cidx + 3] = cast_to<CT>(ko.w);
+        vcache[cidx] = cast_to<CT>(vv.x); vcache[cidx + 1] = cast_to<CT>(vv.y); vcache[cidx + 2] = cast_to<CT>(vv.z); vcache[cidx + 3] = cast_to<CT>(vv.w);
     }
 }
 
-// silu_cpu + hadamard_product_cpu (src/tensor.rs:822-832, :722-734) and the cast before w2.
+// silu_cpu + hadamard_product_cpu (src/tensor.rs:822-832, :722-734) and the cast before w2. grid (column
+// groups, rows); a thread handles four columns (cols is a multiple of 4 here, ld too).
 template <typename OT>
-__global__ void swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t rows, int64_t cols,
-                              OT* __restrict__ out) {
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t cols,
+                                                     OT* __restrict__ out) {
+    const int64_t r = blockIdx.y, c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (c >= cols) return;
+    const float4 v = *reinterpret_cast<const float4*>(a1 + r * ld + c), u = *reinterpret_cast<const float4*>(a3 + r * ld + c);
+    OT* o = out + r * cols + c;
+    o[0] = cast_to<OT>(__fmul_rn(v.x / (1.0f + expf(-v.x)), u.x));
+    o[1] = cast_to<OT>(__fmul_rn(v.y / (1.0f + expf(-v.y)), u.y));
+    o[2] = cast_to<OT>(__fmul_rn(v.z / (1.0f + expf(-v.z)), u.z));
+    o[3] = cast_to<OT>(__fmul_rn(v.w / (1.0f + expf(-v.w)), u.w));
+}
+// general shapes
+template <typename OT>
+__global__ void swiglu_any_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t rows, int64_t cols,
+                                  OT* __restrict__ out) {
     const int64_t count = rows * cols;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / cols, c = i - r * cols;
@@ -83,8 +166,8 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
 }
 
 // Bounded poll of one {value, sequence} entry of the tensor-parallel exchange.
-__device__ __forceinline__ bool ll_poll(const uint2* p, uint32_t seq, float& out) {
-    for (uint32_t i = 0; i < (1u << 20); i++) {
+__device__ __forceinline__ bool ll_poll(const uint2* p, uint32_t seq, float& out, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++) {
         uint32_t v, f;
         asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(p) : "memory");
         if (f == seq) { out = __uint_as_float(v); return true; }
@@ -108,7 +191,7 @@ __device__ __forceinline__ void argmax_block(const float* logits, int n, const S
         bool ok = true;
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             float v;
-            ok = ll_poll(sy.ll_logits + i, seq, v) && ok;
+            ok = ll_poll(sy.ll_logits + i, seq, v, ok ? (1u << 20) : 64u) && ok;  // after one wait ran out the rest give up quickly
             sy.dense_out[i] = v;
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
         }
@@ -254,20 +337,34 @@ int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, in
     return RLB_OK;
 }
 
-int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype, void* out) {
-    if (out_dtype == RLB_F16) rmsnorm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, dim, gain, eps, (__half*)out);
-    else rmsnorm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, dim, gain, eps, (float*)out);
+int launch_add_norm_rows(rlb_ctx* ctx, float* x, const float* y, int round_y, int n, int dim, const float* gain, float eps,
+                         rlb_dtype out_dtype, void* out) {
+    const bool regs = dim % 4 == 0 && dim <= 8192 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)gain) & 15) == 0;
+    if (out_dtype == RLB_F16) {
+        if (regs) add_norm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (__half*)out);
+        else rmsnorm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (__half*)out);
+    } else {
+        if (regs) add_norm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (float*)out);
+        else rmsnorm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (float*)out);
+    }
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
 }
 
+int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype, void* out) {
+    return launch_add_norm_rows(ctx, const_cast<float*>(x), nullptr, 0, n, dim, gain, eps, out_dtype, out);  // (x is not written without y)
+}
+
 int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int64_t ld, int n, int start_pos, int heads, int hd,
                        int max_seq, const float* rope, rlb_dtype cache_dtype, void* kcache, void* vcache) {
+    if (hd % 4 != 0 || ld % 4 != 0 || (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)rope) & 15) != 0)
+        return rlb_fail(RLB_ERR_INVALID, "rope: head_dim %d and the row stride %lld must be multiples of 4", hd, (long long)ld);
+    const dim3 grid(n, (heads + 7) / 8);
     if (cache_dtype == RLB_F16)
-        rope_append_kernel<__half><<<n, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
+        rope_append_kernel<__half><<<grid, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
     else
-        rope_append_kernel<float><<<n, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
+        rope_append_kernel<float><<<grid, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
@@ -276,8 +373,12 @@ int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, i
 int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t ld, int64_t rows, int64_t cols, rlb_dtype out_dtype,
                        void* out) {
     const int64_t count = rows * cols;
-    if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (__half*)out);
-    else swiglu_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (float*)out);
+    if (cols % 4 == 0 && ld % 4 == 0 && rows <= 65535 && (((uintptr_t)a1 | (uintptr_t)a3) & 15) == 0) {
+        const dim3 grid((unsigned)((cols / 4 + 255) / 256), (unsigned)rows);
+        if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid, 256, 0, ctx->stream>>>(a1, a3, ld, cols, (__half*)out);
+        else swiglu_kernel<float><<<grid, 256, 0, ctx->stream>>>(a1, a3, ld, cols, (float*)out);
+    } else if (out_dtype == RLB_F16) swiglu_any_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (__half*)out);
+    else swiglu_any_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (float*)out);
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;

@@ -3,7 +3,8 @@
 // (src/tensor.rs:999-1025, f16 branch :1476-1666; OpenCL kernel matrix_mul_transposed_f16,
 // src/tensor_opencl_support.rs:512-557), the dense contraction of the projections.
 //
-// One persistent kernel, one CTA per SM. A tile is 128 tokens x 256 weight rows: the tokens are the
+// One persistent kernel, one CTA per SM. A tile is 128 tokens x TN weight rows (TN = 256; 128 for prompts of
+// up to 128 tokens, where every tile is split over K and a narrower tile halves the partial results): the tokens are the
 // MMA's M (tensor-memory lanes), the weight rows its N (tensor-memory columns), so a thread of the
 // epilogue owns one token and reads consecutive weight rows -- consecutive addresses of the
 // row-major output.
@@ -41,14 +42,13 @@
 namespace {
 
 constexpr int TM = 128;       // tokens per tile (MMA M)
-constexpr int TN = 256;       // weight rows per tile (MMA N)
+// (weight rows per tile, MMA N: template parameter TN, 256 or 128)
 constexpr int BK = 64;        // K columns per stage in f16 (128 bytes = one swizzle span)
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kTcThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr uint32_t X_BYTES = TM * 128;   // one activation tile of a stage
-constexpr uint32_t W_BYTES = TN * 128;
-constexpr size_t kSlabFloats = (size_t)TM * TN;   // one partial tile
+constexpr int kMaxGrid = 256;            // CTAs of the persistent kernel at most (one per SM)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -120,7 +120,7 @@ struct Sched {
     int whole;             // tiles handed out whole, round-robin (a multiple of the grid size)
     int rest;              // remaining tiles, dealt out by k-block
 };
-__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid) {
+__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid, int TN) {
     Sched s;
     s.n_mt = (n + TM - 1) / TM; s.n_nt = (M + TN - 1) / TN; s.nkb = nkb;
     const int tiles = s.n_mt * s.n_nt;
@@ -186,15 +186,17 @@ template <> struct OutPack<__half> {
     }
 };
 
-template <typename OT, bool TF32>
+template <typename OT, bool TF32, int TN>
 __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x,
                                                                 const __grid_constant__ CUtensorMap tm_x2,
                                                                 const __grid_constant__ CUtensorMap tm_w, OT* __restrict__ C, int64_t ldc,
                                                                 int n, int Mrows, int K, int round_out, float* __restrict__ part, int* err) {
     constexpr int BKE = TF32 ? BK / 2 : BK;                      // K columns of a stage (128 bytes either way)
     constexpr int NX = TF32 ? 2 : 1;                             // activation tiles per stage (hi, lo)
+    constexpr uint32_t W_BYTES = TN * 128;
+    constexpr size_t kSlabFloats = (size_t)TM * TN;              // one partial tile
     constexpr uint32_t STAGE_BYTES = NX * X_BYTES + W_BYTES;
-    constexpr int kStages = kRingBytes / STAGE_BYTES;            // 4 (f16), 3 (tf32)
+    constexpr int kStages = kRingBytes / STAGE_BYTES;            // TN 256: 4 (f16), 3 (tf32); TN 128: 6, 4
     constexpr uint32_t TMEM_COLS = 2 * TN;
 
     extern __shared__ unsigned char smem_raw[];
@@ -209,7 +211,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (K + BKE - 1) / BKE;
-    const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x);
+    const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x, TN);
 
     if (threadIdx.x == 0) {
         dead_flag = 0;
@@ -304,28 +306,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             const int col_base = nt * TN;
             float* slab = p.slot >= 0 ? part + ((size_t)blockIdx.x * 2 + p.slot) * kSlabFloats + (size_t)(q * 32 + lane) * TN : nullptr;
 #pragma unroll 1
-            for (int c0 = 0; c0 < TN; c0 += 16) {
+            for (int c0 = 0; c0 < TN; c0 += 32) {
                 if (col_base + c0 >= Mrows) break;  // (uniform over the warp)
-                uint32_t r[16];
+                // two loads of 16 columns in flight before the wait
+                uint32_t r[2][16];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * TN + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                      "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(taddr));
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(r[h][0]), "=r"(r[h][1]), "=r"(r[h][2]), "=r"(r[h][3]), "=r"(r[h][4]), "=r"(r[h][5]), "=r"(r[h][6]), "=r"(r[h][7]),
+                          "=r"(r[h][8]), "=r"(r[h][9]), "=r"(r[h][10]), "=r"(r[h][11]), "=r"(r[h][12]), "=r"(r[h][13]), "=r"(r[h][14]), "=r"(r[h][15])
+                        : "r"(taddr + 16 * h));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float v[16];
 #pragma unroll
-                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-                if (slab) {
+                for (int h = 0; h < 2; h++) {
+                    const int cc = c0 + 16 * h;
+                    float v[16];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(slab + c0)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else if (token < n) {
-                    if (round_out) {
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[h][j]);
+                    if (slab) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) v[j] = __half2float(__float2half_rn(v[j]));
+                        for (int j = 0; j < 4; j++) reinterpret_cast<float4*>(slab + cc)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else if (token < n && col_base + cc < Mrows) {
+                        if (round_out) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) v[j] = __half2float(__float2half_rn(v[j]));
+                        }
+                        OutPack<OT>::store16(C + (int64_t)token * ldc + col_base + cc, v, vec_c, Mrows - (col_base + cc));
                     }
-                    OutPack<OT>::store16(C + (int64_t)token * ldc + col_base + c0, v, vec_c, Mrows - (col_base + c0));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -343,44 +352,76 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 }
 
 // Second pass for the tiles that were dealt out by k-block: out = cast(round?(sum of the tile's partial tiles
-// in k order)). grid (remaining tiles, 8 row groups of 16 tokens).
-template <typename OT>
+// in k order)). grid (remaining tiles, TM / 8 groups of 8 token rows). The CTAs whose runs meet the tile are
+// found by all threads at once (thread c looks at CTA c); they are consecutive, and their order is the k order.
+template <typename OT, int TN>
 __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ part, OT* __restrict__ C, int64_t ldc, int n, int Mrows,
                                                             int nkb, int grid, int round_out) {
-    const Sched s = make_sched(n, Mrows, nkb, grid);
+    constexpr size_t kSlabFloats = (size_t)TM * TN;
+    __shared__ int seg_slab[kMaxGrid];   // slab index (cta * 2 + slot) of CTA c's piece of this tile, or -1
+    __shared__ int c_lo_s, c_hi_s;
+    const Sched s = make_sched(n, Mrows, nkb, grid, TN);
     const int j = blockIdx.x;
     const long long u_first = (long long)j * s.nkb, u_last = u_first + s.nkb;
-    // the CTAs whose runs meet this tile: c_lo is the last one that starts at or before the tile's first unit
-    int c_lo = (int)(u_first * grid / ((long long)s.rest * s.nkb));
-    if (c_lo > grid - 1) c_lo = grid - 1;
-    while (c_lo + 1 < grid && rest_begin(s, c_lo + 1, grid) <= u_first) c_lo++;
-    while (c_lo > 0 && rest_begin(s, c_lo, grid) > u_first) c_lo--;
-    int c_hi = c_lo;  // inclusive
-    while (c_hi + 1 < grid && rest_begin(s, c_hi + 1, grid) < u_last) c_hi++;
-    if (c_lo == c_hi) return;  // one CTA computed the whole tile and stored it itself
+    if (threadIdx.x == 0) { c_lo_s = grid; c_hi_s = -1; }
+    __syncthreads();
+    for (int c = threadIdx.x; c < grid; c += blockDim.x) {
+        const long long b = rest_begin(s, c, grid), e = rest_begin(s, c + 1, grid);
+        int slab = -1;
+        if (e > b && b < u_last && e > u_first) {   // CTA c's run meets the tile
+            slab = c * 2 + (b >= u_first ? 0 : 1);  // the piece starts the run, or follows a tile boundary inside it
+            atomicMin(&c_lo_s, c);
+            atomicMax(&c_hi_s, c);
+        }
+        seg_slab[c] = slab;
+    }
+    __syncthreads();
+    const int c_lo = c_lo_s, c_hi = c_hi_s;
+    if (c_lo >= c_hi) return;  // one CTA computed the whole tile and stored it itself
     const int tile = s.whole + j;
     const int nt = tile / s.n_mt, mt = tile - nt * s.n_mt;
-    const int row0 = blockIdx.y * 16;
-    for (int e = threadIdx.x; e < 16 * (TN / 4); e += 256) {
+    const int row0 = blockIdx.y * 8;
+    const bool vec_c = ((ldc * (int64_t)sizeof(OT)) % 16 == 0) && (((uintptr_t)C & 15) == 0);
+    for (int e = threadIdx.x; e < 8 * (TN / 4); e += 256) {
         const int rr = row0 + e / (TN / 4), c4 = (e % (TN / 4)) * 4;
         const int token = mt * TM + rr, col = nt * TN + c4;
         if (token >= n || col >= Mrows) continue;
+        const float* src = part + (size_t)rr * TN + c4;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = c_lo; c <= c_hi; c++) {
-            const long long b = rest_begin(s, c, grid);
-            if (rest_begin(s, c + 1, grid) <= b) continue;  // a CTA without units
-            const int slot = (b >= u_first) ? 0 : 1;        // the piece starts the CTA's run, or follows a tile boundary inside it
-            const float4 t = *reinterpret_cast<const float4*>(part + ((size_t)c * 2 + slot) * kSlabFloats + (size_t)rr * TN + c4);
-            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-        }
-        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+        int c = c_lo;
+        for (; c + 3 <= c_hi; c += 4) {   // four partial tiles in flight; added in k order
+            float4 t[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            if (round_out) v[q] = __half2float(__float2half_rn(v[q]));
-            if (col + q < Mrows) {
-                if (sizeof(OT) == 4) reinterpret_cast<float*>(C)[(int64_t)token * ldc + col + q] = v[q];
-                else reinterpret_cast<__half*>(C)[(int64_t)token * ldc + col + q] = __float2half_rn(v[q]);
+            for (int k = 0; k < 4; k++)
+                t[k] = seg_slab[c + k] >= 0 ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)seg_slab[c + k] * kSlabFloats)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { acc.x += t[k].x; acc.y += t[k].y; acc.z += t[k].z; acc.w += t[k].w; }
+        }
+        for (; c <= c_hi; c++)
+            if (seg_slab[c] >= 0) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (size_t)seg_slab[c] * kSlabFloats));
+                acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
             }
+        float v[4] = {acc.x, acc.y, acc.z, acc.w};
+        if (round_out) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[q] = __half2float(__float2half_rn(v[q]));
+        }
+        OT* dst = C + (int64_t)token * ldc + col;
+        if (vec_c && col + 4 <= Mrows) {
+            if (sizeof(OT) == 4) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            else {
+                const uint32_t w0 = (uint32_t)__half_as_ushort(__float2half_rn(v[0])) | ((uint32_t)__half_as_ushort(__float2half_rn(v[1])) << 16);
+                const uint32_t w1 = (uint32_t)__half_as_ushort(__float2half_rn(v[2])) | ((uint32_t)__half_as_ushort(__float2half_rn(v[3])) << 16);
+                *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                if (col + q < Mrows) {
+                    if (sizeof(OT) == 4) reinterpret_cast<float*>(dst)[q] = v[q];
+                    else reinterpret_cast<__half*>(dst)[q] = __float2half_rn(v[q]);
+                }
         }
     }
 }
@@ -439,15 +480,16 @@ __global__ void tf32_split_kernel(const float* __restrict__ x, int64_t ldx, int 
     }
 }
 
-template <typename OT, bool TF32>
-int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
+template <typename OT, bool TF32, int TN>
+int launch_tn(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
               int* err) {
-    RLB_TRY(load_encode());
     constexpr int BKE = TF32 ? BK / 2 : BK;
+    constexpr size_t kSlabFloats = (size_t)TM * TN;
     const int nkb = (K + BKE - 1) / BKE;
     const long long units = (long long)((n + TM - 1) / TM) * ((M + TN - 1) / TN) * nkb;
-    const int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
-    const Sched sched = make_sched(n, M, nkb, grid);
+    const int max_grid = ctx->sm_count < kMaxGrid ? ctx->sm_count : kMaxGrid;
+    const int grid = (int)(units < max_grid ? units : max_grid);
+    const Sched sched = make_sched(n, M, nkb, grid, TN);
     // scratch: [x hi | x lo] for the f32 form, then two partial tiles per CTA (only touched when tiles are dealt out by k-block)
     const size_t xs = TF32 ? (((size_t)n * K * sizeof(float) + 255) & ~(size_t)255) : 0;
     const size_t slabs = sched.rest > 0 ? (size_t)grid * 2 * kSlabFloats * sizeof(float) : 0;
@@ -471,7 +513,7 @@ int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
         tx2 = tx;
     }
     const size_t smem = (size_t)kRingBytes + 1024;
-    auto kern = gemm_tc_kernel<OT, TF32>;
+    auto kern = gemm_tc_kernel<OT, TF32, TN>;
     static std::atomic<uint64_t> set{0};
     if (!attr_done(set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -481,11 +523,22 @@ int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
     RLB_LAUNCH_CHECK();
     count_launch(ctx);
     if (sched.rest > 0) {
-        gemm_tc_fixup_kernel<OT><<<dim3(sched.rest, TM / 16), 256, 0, ctx->stream>>>(part, C, ldc, n, M, nkb, grid, round_out);
+        gemm_tc_fixup_kernel<OT, TN><<<dim3(sched.rest, TM / 8), 256, 0, ctx->stream>>>(part, C, ldc, n, M, nkb, grid, round_out);
         RLB_LAUNCH_CHECK();
         count_launch(ctx);
     }
     return RLB_OK;
+}
+
+template <typename OT, bool TF32>
+int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
+              int* err) {
+    RLB_TRY(load_encode());
+    // 256-row tiles where whole tiles can be handed out; 128-row tiles when there are fewer tiles than SMs, where
+    // every tile is split over K anyway and the narrower tile halves the partial results
+    const long long tiles256 = (long long)((n + TM - 1) / TM) * ((M + 255) / 256);
+    if (tiles256 < ctx->sm_count) return launch_tn<OT, TF32, 128>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    return launch_tn<OT, TF32, 256>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
 }
 
 }  // namespace

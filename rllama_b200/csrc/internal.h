@@ -179,6 +179,9 @@ int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, in
 // a[n][dim] (weight dtype) = cast(rmsnorm(x) * gain)
 int launch_rmsnorm_rows(rlb_ctx* ctx, const float* x, int n, int dim, const float* gain, float eps, rlb_dtype out_dtype,
                         void* out);
+// x[n][dim] += round_f16?(y) (y may be null: no add), then a = cast(rmsnorm(x) * gain)
+int launch_add_norm_rows(rlb_ctx* ctx, float* x, const float* y, int round_y, int n, int dim, const float* gain, float eps,
+                         rlb_dtype out_dtype, void* out);
 // q,k,v: n rows of nq f32 GEMM outputs (already rounded when f16), row stride ld. Rotates q in place, writes K (rotated)
 // and V to the cache.
 int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, int64_t ld, int n, int start_pos, int heads,

@@ -110,6 +110,7 @@ struct rlb_model {
     size_t xbuf_bytes = 0;
     char* peer_xbuf[RLB_MAX_TP] = {nullptr};  // peer_xbuf[rank] == xbuf
     bool peers_open = false;
+    bool peers_ipc = false;          // the peer buffers were mapped from IPC handles (and must be unmapped)
     uint64_t graph_gen = 0;          // bumped when captured graphs become stale
 
     // options / statistics
@@ -406,12 +407,16 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
     const int round_proj = (f16 && m->tp == 1) ? 1 : 0;  // with tensor parallelism the rounding follows the reduction
     RLB_TRY(launch_embed(ctx, m->tok_emb, m->pf_tokens, n, d, m->pf_x));
 
+    // The residual add of a projection's output (src/transformer.rs:442-445) is folded into the RMSNorm that follows
+    // it: `pending` says that pf_p holds a projection output not yet added to the residual rows.
+    bool pending = false;
+    const int round_add = (f16 && !round_proj) ? 1 : 0;
     for (int l = 0; l < m->p.n_layers; l++) {
         const LayerW& W = m->L[l];
         char* kc = (char*)c->k + (size_t)l * c->layer_elems * m->wsz;
         char* vc = (char*)c->v + (size_t)l * c->layer_elems * m->wsz;
         if (W.host) RLB_CUDA(cudaMemcpyAsync(m->stage, W.host, m->layer_bytes, cudaMemcpyHostToDevice, ctx->stream));
-        RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.attn_norm, m->p.norm_eps, m->wdt, m->pf_a));
+        RLB_TRY(launch_add_norm_rows(ctx, m->pf_x, pending ? m->pf_p : nullptr, round_add, n, d, W.attn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         // q, k and v in one GEMM: row i of the result is [q_i | k_i | v_i]
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.wqkv, d, m->pf_qkv, 3 * nq, n, 3 * nq, d, f16, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(launch_rope_append(ctx, m->pf_qkv, m->pf_qkv + nq, m->pf_qkv + 2 * nq, 3 * nq, n, start_pos, m->nh, m->hd,
@@ -422,15 +427,16 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
         RLB_TRY(launch_attn_prefill(ctx, m->wdt, aa));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_o, nq, W.wo, nq, m->pf_p, d, n, d, nq, round_proj, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
-        RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
-        RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
+        RLB_TRY(launch_add_norm_rows(ctx, m->pf_x, m->pf_p, round_add, n, d, W.ffn_norm, m->p.norm_eps, m->wdt, m->pf_a));
         // w1 and w3 (stored back to back) in one GEMM: row i of the result is [w1 x_i | w3 x_i]
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_a, d, W.w1, d, m->pf_g1, 2 * F, n, 2 * F, d, f16, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(launch_swiglu_rows(ctx, m->pf_g1, m->pf_g1 + F, 2 * F, n, F, m->wdt, m->pf_g));
         RLB_TRY(launch_gemm_nt(ctx, m->wdt, m->pf_g, F, W.w2, F, m->pf_p, d, n, d, F, round_proj, m->scalars + 8, m->w_f16_exact));
         RLB_TRY(tp_reduce(m, m->pf_p, (size_t)n * d, false));
-        RLB_TRY(launch_add_rows(ctx, m->pf_x, m->pf_p, (int64_t)n * d, f16 && !round_proj));
+        pending = true;
     }
+    // the last layer's FFN output still has to be added; only the last row is needed from here on
+    RLB_TRY(launch_add_rows(ctx, m->pf_x + (size_t)(n - 1) * d, m->pf_p + (size_t)(n - 1) * d, d, round_add));
     // only the last row gets logits (src/transformer.rs:378-381)
     RLB_TRY(launch_rmsnorm_rows(ctx, m->pf_x + (size_t)(n - 1) * d, 1, d, m->norm, m->p.norm_eps, RLB_F32, m->pf_last));
     GemvArgs a;
@@ -689,7 +695,7 @@ int rlb_model_free(rlb_model* m) {
     cudaStreamSynchronize(ctx->stream);
     nccl_destroy(&m->nccl);
     for (int r = 0; r < m->tp; r++)
-        if (m->peers_open && r != m->rank && m->peer_xbuf[r]) cudaIpcCloseMemHandle(m->peer_xbuf[r]);
+        if (m->peers_open && m->peers_ipc && r != m->rank && m->peer_xbuf[r]) cudaIpcCloseMemHandle(m->peer_xbuf[r]);
     if (m->xbuf) cudaFree(m->xbuf);
     void* ptrs[] = {m->tok_emb, m->norm, m->output, m->rope, m->xa, m->xb, m->qbuf, m->obuf, m->gbuf, m->part_wo, m->part_w2,
                     m->logits_local, m->logits, m->scalars, m->tokens_out, m->attn_scratch, m->attn_counters, m->pf_tokens, m->pf_x,
@@ -760,6 +766,43 @@ int rlb_tp_peer_import(rlb_model* m, const void* handles, int32_t n_handles) {
         m->peer_xbuf[r] = (char*)p;
     }
     m->peers_open = true;
+    m->peers_ipc = true;
+    return RLB_OK;
+}
+
+int rlb_tp_peer_import_local(rlb_model* m, rlb_model* const* peers, int32_t n_peers) {
+    if (!m || !peers) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import_local: null pointer");
+    if (n_peers != m->tp) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import_local: %d models for %d ranks", n_peers, m->tp);
+    if (m->tp == 1) return rlb_fail(RLB_ERR_STATE, "rlb_tp_peer_import_local: the model is not tensor parallel");
+    if (m->peers_open) return RLB_OK;
+    for (int r = 0; r < m->tp; r++) {
+        rlb_model* p = r == m->rank ? m : peers[r];
+        if (!p) return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import_local: no model for rank %d", r);
+        if (p->tp != m->tp || p->rank != r || p->p.dim != m->p.dim || p->p.n_layers != m->p.n_layers || p->p.vocab_size != m->p.vocab_size)
+            return rlb_fail(RLB_ERR_INVALID, "rlb_tp_peer_import_local: model %d is not rank %d of the same %d-way model", r, r, m->tp);
+        {   // the peer's exchange buffer, allocated on its own device
+            std::lock_guard<std::recursive_mutex> g(p->ctx->mu);
+            RLB_CUDA(cudaSetDevice(p->ctx->device));
+            if (!p->xbuf) {
+                p->xbuf_bytes = xb_total(p);
+                RLB_TRY(dev_alloc((void**)&p->xbuf, p->xbuf_bytes));
+                RLB_CUDA(cudaMemset(p->xbuf, 0, p->xbuf_bytes));
+            }
+        }
+        std::lock_guard<std::recursive_mutex> g(m->ctx->mu);
+        RLB_CUDA(cudaSetDevice(m->ctx->device));
+        if (p->ctx->device != m->ctx->device) {
+            int can = 0;
+            RLB_CUDA(cudaDeviceCanAccessPeer(&can, m->ctx->device, p->ctx->device));
+            if (!can) return rlb_fail(RLB_ERR_COMM, "device %d cannot access the memory of device %d", m->ctx->device, p->ctx->device);
+            cudaError_t e = cudaDeviceEnablePeerAccess(p->ctx->device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (e != cudaSuccess) return rlb_fail(RLB_ERR_COMM, "cudaDeviceEnablePeerAccess(%d): %s", p->ctx->device, cudaGetErrorString(e));
+        }
+        m->peer_xbuf[r] = p->xbuf;
+    }
+    m->peers_open = true;
+    m->peers_ipc = false;
     return RLB_OK;
 }
 
@@ -905,7 +948,10 @@ int rlb_decode_greedy(rlb_model* m, rlb_caches* c, int32_t first_token, int32_t 
     RLB_CUDA(cudaMemcpyAsync(m->scalars, m->h_scalars, 4 * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
     cudaGraphExec_t& slot = c->graph_adv;
     int done = 0;
-    if (!c->warmed) {  // the eager first step is not part of the timed region
+    // Not part of the timed region: the eager first step on fresh caches and, under tensor parallelism, one
+    // step after which the ranks are aligned by the exchange itself (else the skew the host left between
+    // the ranks' launches is timed)
+    if (!c->warmed || (m->tp > 1 && n_steps > 1)) {
         RLB_TRY(run_decode_step(m, c, true, &slot));
         done = 1;
     }

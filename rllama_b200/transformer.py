@@ -5,6 +5,7 @@ reference so that tests read like its own.
 """
 import ctypes
 import sys
+import weakref
 
 import numpy as np
 
@@ -130,6 +131,11 @@ class Transformer:
         blob = b"".join(handles)
         check(_ffi.lib().rlb_tp_peer_import(self._h, ctypes.c_char_p(blob), len(handles)))
 
+    def peer_import_local(self, models):
+        """Peer exchange buffers of ranks that live in this process: the models of all ranks, by rank."""
+        arr = (ctypes.c_void_p * len(models))(*[m._h for m in models])
+        check(_ffi.lib().rlb_tp_peer_import_local(self._h, arr, len(models)))
+
     def set_tp_mode(self, mode):
         check(_ffi.lib().rlb_tp_set_mode(self._h, {"nccl": 0, "push": 1}.get(mode, mode)))
 
@@ -170,6 +176,9 @@ class Transformer:
 
     def free(self):
         if getattr(self, "_h", None):
+            # caches refer to their model inside the library: they go first
+            for c in list(getattr(self, "_caches", ())):
+                c.free()
             _ffi.lib().rlb_model_free(self._h)
             self._h = ctypes.c_void_p()
 
@@ -192,6 +201,9 @@ class TransformerCaches:
             check(_ffi.lib().rlb_caches_create(transformer._h, ctypes.byref(self._h)))
         else:
             self._h = _handle
+        if not hasattr(transformer, "_caches"):
+            transformer._caches = weakref.WeakSet()
+        transformer._caches.add(self)
 
     def true_clone(self):
         h = ctypes.c_void_p()

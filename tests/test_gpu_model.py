@@ -205,8 +205,10 @@ def test_prefill_equals_token_by_token_and_chunked(cuda_ctx):
     gpu.forward(long_toks[:37], 0, c4)
     chunked3 = gpu.forward(long_toks[37:], 37, c4)
     assert rel_err(chunked3, full3) <= F32_REL
+    # the cache rows agree to f32 rounding (the GEMM's K split depends on the number of token tiles, so the
+    # summation order of a 150-row call and a 113-row call differs)
     k_full, k_chunk = c3.read("k", 1, 3, 149), c4.read("k", 1, 3, 149)
-    assert np.array_equal(k_full, k_chunk)
+    assert np.abs(k_full - k_chunk).max() <= 1e-5 * np.abs(k_full).max()
 
 
 def test_device_greedy_loop_equals_host_loop(cuda_ctx):
@@ -283,6 +285,34 @@ def test_percentage_to_gpu_gives_identical_logits(cuda_ctx, f16):
     for key, (logits, toks) in runs.items():
         assert np.array_equal(logits, ref_logits), key
         assert np.array_equal(toks, ref_toks), key
+
+
+def test_exchange_wait_runs_out_and_reports(cuda_ctx):
+    """A tensor-parallel rank whose peer never sends: the bounded wait of the push exchange runs out, the
+    kernels return, forward reports a communication error (status 6) and the context stays usable. Both
+    "ranks" are models in this process on one GPU; only rank 0 ever runs, so no kernel waits on another."""
+    from rllama_b200 import DataSettings, F32, Transformer
+    cfg = cfg_variant("tiny", dim=256, n_heads=4, ffn=512, n_layers=1, vocab=1024, max_seq_len=16)
+    ranks = []
+    for r in range(2):
+        m = Transformer(cfg["dim"], 1, cfg["n_heads"], cfg["ffn"], cfg["vocab"], cfg["max_seq_len"], cfg["norm_eps"],
+                        DataSettings(cl=cuda_ctx).force_f16(), tp_rank=r, tp_size=2)
+        S.load_into(m, cfg)
+        m.finalize()
+        ranks.append(m)
+    ranks[0].peer_import_local(ranks)
+    ranks[0].set_tp_mode("push")
+    c = ranks[0].make_caches()
+    with pytest.raises(RllamaError) as e:
+        ranks[0].forward([5], 0, c)   # one token: the decode chain, whose exchanges wait for rank 1
+    assert e.value.status == 6 and "another rank" in str(e.value)
+    # the context is intact: an unrelated op still runs and gives the right answer
+    t = cuda_ctx.upload(np.arange(12, dtype=np.float32).reshape(3, 4))
+    u = cuda_ctx.zeros(4, 3, F32)
+    u.transpose_from(t)
+    assert np.array_equal(u.to_numpy(), np.arange(12, dtype=np.float32).reshape(3, 4).T)
+    for m in ranks:
+        m.free()
 
 
 def test_construction_errors(cuda_ctx):
