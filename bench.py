@@ -313,20 +313,27 @@ def measure(model, cfg, cl, D, local_rank, K, Wm, do_e2e=True):
 
     if do_e2e:
         # end-to-end loop through Transformer.forward with host buffers
+        def margin(lg):  # gap between the two largest logits: how close the greedy choice was
+            top2 = np.partition(lg, -2)[-2:]
+            return float(top2[1] - top2[0])
         c2 = model.make_caches()
         logits = model.forward(prompt, 0, c2)
+        margins = [margin(logits)]
         tok = int(np.argmax(logits))
         pos = P
         for _ in range(Wm):
-            logits = model.forward([tok], pos, c2); tok = int(np.argmax(logits)); pos += 1
+            logits = model.forward([tok], pos, c2); margins.append(margin(logits)); tok = int(np.argmax(logits)); pos += 1
         D.barrier(cl)
         t0 = time.perf_counter()
         for _ in range(K):
             logits = model.forward([tok], pos, c2)
+            if len(margins) < 32:
+                margins.append(margin(logits))
             tok = int(np.argmax(logits))
             pos += 1
         D.barrier(cl)
         e2e_ms = D.max((time.perf_counter() - t0) * 1e3)
+        out["margins"] = margins
         out["e2e"] = {"value": 1e3 * K / e2e_ms, "unit": UNIT, "ms_per_token": e2e_ms / K, "h2d_bytes_per_step": 8,
                       "d2h_bytes_per_step": 4 * cfg["vocab"]}
         c2.free()
@@ -480,7 +487,9 @@ def main():
             "l2": "inputs larger than L2 (every step streams all weights)", "prefill_ms": m["prefill_ms"],
             "prefill_tflops_per_gpu": prefill_flops(cfg, m["P"]) / (m["prefill_ms"] * 1e-3) / 1e12 / world,
             # all decoded tokens (first after the prompt, warm-up, timed): same seed and warm-up at every N
-            "tokens_sha1": hashlib.sha1(m["tokens"].tobytes()).hexdigest(), "tokens_head": [int(t) for t in m["tokens"][:16]],
+            "tokens_sha1": hashlib.sha1(m["tokens"].tobytes()).hexdigest(), "tokens_head": [int(t) for t in m["tokens"][:26]],
+            # top-2 logit gap behind each of those tokens: f16 sequences of different N part ways only at a near-tie
+            "top2_margin_head": [round(x, 5) for x in m.get("margins", [])[:26]],
             "ranks_agree": {"tokens": m["ranks_agree_tokens"], "last_logits_max_abs_diff": m.get("ranks_logit_max_abs_diff")},
         })
         if also:

@@ -211,6 +211,8 @@ template <typename CT>
 __global__ void __launch_bounds__(kThreads) attn_prefill_kernel(const AttnPrefillArgs a) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[kWarps];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int hd = a.hd, head = blockIdx.x, i = blockIdx.y;
     const int T = a.start_pos + i + 1;  // mask: col >= row + start_pos + 1 is -inf
     float* q_sh = sm;
@@ -249,6 +251,8 @@ __global__ void __launch_bounds__(256) attn_prefill_tiled_kernel(const AttnPrefi
     float* k_s = q_s + kQB * LD;           // [kTB][LD]
     float* v_s = k_s + kTB * LD;           // [kTB][HD]
     float* p_s = v_s + kTB * HD;           // [kQB][PL]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, i0 = blockIdx.y * kQB;
     const int tid = threadIdx.x, r = tid >> 3, g = tid & 7;
     const int rows = min(kQB, a.n - i0);
@@ -676,8 +680,14 @@ int launch_attn_prefill(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnPrefillAr
         if (cache_dtype == RLB_F16) kern = a.hd == 128 ? (const void*)attn_prefill_tiled_kernel<__half, 128> : (const void*)attn_prefill_tiled_kernel<__half, 64>;
         else kern = a.hd == 128 ? (const void*)attn_prefill_tiled_kernel<float, 128> : (const void*)attn_prefill_tiled_kernel<float, 64>;
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = grid; lc.blockDim = dim3(256); lc.dynamicSmemBytes = smem; lc.stream = ctx->stream;
+        cudaLaunchAttribute pattr[1];
+        pattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pattr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = pattr; lc.numAttrs = ctx->pdl_chain ? 1 : 0;
         void* kargs[] = {(void*)&a};
-        RLB_CUDA(cudaLaunchKernel(kern, grid, dim3(256), kargs, smem, ctx->stream));
+        RLB_CUDA(cudaLaunchKernelExC(&lc, kern, kargs));
         count_launch(ctx);
         return RLB_OK;
     }

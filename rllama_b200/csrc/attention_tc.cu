@@ -196,6 +196,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // the set-up above overlaps the previous kernel's tail; q and the cache rows are its outputs
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     // the query block, split into halves, in the A-operand layout: row r, 16-byte chunk c of a 64-column
     // block lands at r * 128 + ((c ^ (r & 7)) * 16)
     if (warp < kSoftmaxWarps) {
@@ -456,8 +459,7 @@ int launch_hd(rlb_ctx* ctx, const CUtensorMap& mk, const CUtensorMap& mv, const 
         attr_mark(set, ctx->device);
     }
     dim3 grid(args.heads, (args.n + QB - 1) / QB);
-    kern<<<grid, kThreadsTc, smem, ctx->stream>>>(mk, mv, args);
-    RLB_LAUNCH_CHECK();
+    RLB_CUDA(rlb_launch(kern, grid, dim3(kThreadsTc), smem, ctx, mk, mv, args));
     count_launch(ctx);
     return RLB_OK;
 }

@@ -19,6 +19,8 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 
 // Embedding::get_embedding + Tensor::concat (src/embedding.rs:50-52, src/tensor.rs:736-766)
 __global__ void embed_kernel(const float* __restrict__ table, const int32_t* __restrict__ tokens, int dim, float* __restrict__ x) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     const int row = blockIdx.x;
     const float4* src = reinterpret_cast<const float4*>(table + (int64_t)tokens[row] * dim);
     float4* dst = reinterpret_cast<float4*>(x + (int64_t)row * dim);
@@ -31,6 +33,8 @@ __global__ void embed_kernel(const float* __restrict__ table, const int32_t* __r
 template <typename OT>
 __global__ void __launch_bounds__(256) add_norm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int do_round, int dim,
                                                             const float* __restrict__ gain, float eps, OT* __restrict__ out) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     constexpr int G = 8;  // float4 groups per thread: 8 * 4 * 256 = 8192 elements
     __shared__ float red[8];
     float* xr = x + (int64_t)blockIdx.x * dim;
@@ -84,6 +88,8 @@ __global__ void __launch_bounds__(256) add_norm_rows_kernel(float* __restrict__ 
 template <typename OT>
 __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int do_round, int dim, const float* __restrict__ gain,
                                     float eps, OT* __restrict__ out) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     __shared__ float red[32];
     float* xr = x + (int64_t)blockIdx.x * dim;
     float ss = 0.f;
@@ -113,6 +119,8 @@ template <typename CT>
 __global__ void __launch_bounds__(256) rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int64_t ld,
                                                           int start_pos, int heads, int hd, int max_seq, const float* __restrict__ rope,
                                                           CT* __restrict__ kcache, CT* __restrict__ vcache) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     const int i = blockIdx.x, pos = start_pos + i;
     const int head = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= heads) return;
@@ -138,6 +146,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(float* __restrict__ q,
 template <typename OT>
 __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t cols,
                                                      OT* __restrict__ out) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     const int64_t r = blockIdx.y, c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     if (c >= cols) return;
     const float4 v = *reinterpret_cast<const float4*>(a1 + r * ld + c), u = *reinterpret_cast<const float4*>(a3 + r * ld + c);
@@ -151,6 +161,8 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ a
 template <typename OT>
 __global__ void swiglu_any_kernel(const float* __restrict__ a1, const float* __restrict__ a3, int64_t ld, int64_t rows, int64_t cols,
                                   OT* __restrict__ out) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     const int64_t count = rows * cols;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / cols, c = i - r * cols;
@@ -161,6 +173,8 @@ __global__ void swiglu_any_kernel(const float* __restrict__ a1, const float* __r
 }
 
 __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t count, int do_round) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
         x[i] += do_round ? round_f16(y[i]) : y[i];
 }
@@ -331,8 +345,7 @@ inline int grid_for(int64_t n, int block = 256, int cap = 148 * 8) {
 }  // namespace
 
 int launch_embed(rlb_ctx* ctx, const float* table, const int32_t* tokens_dev, int n, int dim, float* x) {
-    embed_kernel<<<n, 256, 0, ctx->stream>>>(table, tokens_dev, dim, x);
-    RLB_LAUNCH_CHECK();
+    RLB_CUDA(rlb_launch(embed_kernel, dim3(n), dim3(256), 0, ctx, table, tokens_dev, dim, x));
     count_launch(ctx);
     return RLB_OK;
 }
@@ -341,13 +354,12 @@ int launch_add_norm_rows(rlb_ctx* ctx, float* x, const float* y, int round_y, in
                          rlb_dtype out_dtype, void* out) {
     const bool regs = dim % 4 == 0 && dim <= 8192 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)gain) & 15) == 0;
     if (out_dtype == RLB_F16) {
-        if (regs) add_norm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (__half*)out);
-        else rmsnorm_rows_kernel<__half><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (__half*)out);
+        if (regs) RLB_CUDA(rlb_launch(add_norm_rows_kernel<__half>, dim3(n), dim3(256), 0, ctx, x, y, round_y, dim, gain, eps, (__half*)out));
+        else RLB_CUDA(rlb_launch(rmsnorm_rows_kernel<__half>, dim3(n), dim3(256), 0, ctx, x, y, round_y, dim, gain, eps, (__half*)out));
     } else {
-        if (regs) add_norm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (float*)out);
-        else rmsnorm_rows_kernel<float><<<n, 256, 0, ctx->stream>>>(x, y, round_y, dim, gain, eps, (float*)out);
+        if (regs) RLB_CUDA(rlb_launch(add_norm_rows_kernel<float>, dim3(n), dim3(256), 0, ctx, x, y, round_y, dim, gain, eps, (float*)out));
+        else RLB_CUDA(rlb_launch(rmsnorm_rows_kernel<float>, dim3(n), dim3(256), 0, ctx, x, y, round_y, dim, gain, eps, (float*)out));
     }
-    RLB_LAUNCH_CHECK();
     count_launch(ctx);
     return RLB_OK;
 }
@@ -362,10 +374,9 @@ int launch_rope_append(rlb_ctx* ctx, float* q, const float* k, const float* v, i
         return rlb_fail(RLB_ERR_INVALID, "rope: head_dim %d and the row stride %lld must be multiples of 4", hd, (long long)ld);
     const dim3 grid(n, (heads + 7) / 8);
     if (cache_dtype == RLB_F16)
-        rope_append_kernel<__half><<<grid, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache);
+        RLB_CUDA(rlb_launch(rope_append_kernel<__half>, grid, dim3(256), 0, ctx, q, k, v, ld, start_pos, heads, hd, max_seq, rope, (__half*)kcache, (__half*)vcache));
     else
-        rope_append_kernel<float><<<grid, 256, 0, ctx->stream>>>(q, k, v, ld, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache);
-    RLB_LAUNCH_CHECK();
+        RLB_CUDA(rlb_launch(rope_append_kernel<float>, grid, dim3(256), 0, ctx, q, k, v, ld, start_pos, heads, hd, max_seq, rope, (float*)kcache, (float*)vcache));
     count_launch(ctx);
     return RLB_OK;
 }
@@ -375,18 +386,16 @@ int launch_swiglu_rows(rlb_ctx* ctx, const float* a1, const float* a3, int64_t l
     const int64_t count = rows * cols;
     if (cols % 4 == 0 && ld % 4 == 0 && rows <= 65535 && (((uintptr_t)a1 | (uintptr_t)a3) & 15) == 0) {
         const dim3 grid((unsigned)((cols / 4 + 255) / 256), (unsigned)rows);
-        if (out_dtype == RLB_F16) swiglu_kernel<__half><<<grid, 256, 0, ctx->stream>>>(a1, a3, ld, cols, (__half*)out);
-        else swiglu_kernel<float><<<grid, 256, 0, ctx->stream>>>(a1, a3, ld, cols, (float*)out);
-    } else if (out_dtype == RLB_F16) swiglu_any_kernel<__half><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (__half*)out);
-    else swiglu_any_kernel<float><<<grid_for(count), 256, 0, ctx->stream>>>(a1, a3, ld, rows, cols, (float*)out);
-    RLB_LAUNCH_CHECK();
+        if (out_dtype == RLB_F16) RLB_CUDA(rlb_launch(swiglu_kernel<__half>, grid, dim3(256), 0, ctx, a1, a3, ld, cols, (__half*)out));
+        else RLB_CUDA(rlb_launch(swiglu_kernel<float>, grid, dim3(256), 0, ctx, a1, a3, ld, cols, (float*)out));
+    } else if (out_dtype == RLB_F16) RLB_CUDA(rlb_launch(swiglu_any_kernel<__half>, dim3(grid_for(count)), dim3(256), 0, ctx, a1, a3, ld, rows, cols, (__half*)out));
+    else RLB_CUDA(rlb_launch(swiglu_any_kernel<float>, dim3(grid_for(count)), dim3(256), 0, ctx, a1, a3, ld, rows, cols, (float*)out));
     count_launch(ctx);
     return RLB_OK;
 }
 
 int launch_add_rows(rlb_ctx* ctx, float* x, const float* y, int64_t count, int round_f16_flag) {
-    add_rows_kernel<<<grid_for(count), 256, 0, ctx->stream>>>(x, y, count, round_f16_flag);
-    RLB_LAUNCH_CHECK();
+    RLB_CUDA(rlb_launch(add_rows_kernel, dim3(grid_for(count)), dim3(256), 0, ctx, x, y, count, round_f16_flag));
     count_launch(ctx);
     return RLB_OK;
 }

@@ -37,6 +37,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace {
@@ -45,9 +47,10 @@ constexpr int TM = 128;       // tokens per tile (MMA M)
 // (weight rows per tile, MMA N: template parameter TN, 256 or 128)
 constexpr int BK = 64;        // K columns per stage in f16 (128 bytes = one swizzle span)
 constexpr int kRingBytes = 192 * 1024;
-constexpr int kTcThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+// threads: warp 0 TMA, warp 1 MMA, then four epilogue warps per 128-token block of a tile
+constexpr int tc_threads(int mt) { return 64 + 128 * mt; }
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr uint32_t X_BYTES = TM * 128;   // one activation tile of a stage
+constexpr uint32_t X_BYTES = TM * 128;   // one 128-token activation block of a stage
 constexpr int kMaxGrid = 256;            // CTAs of the persistent kernel at most (one per SM)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -120,9 +123,9 @@ struct Sched {
     int whole;             // tiles handed out whole, round-robin (a multiple of the grid size)
     int rest;              // remaining tiles, dealt out by k-block
 };
-__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid, int TN) {
+__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid, int TN, int tile_tokens) {
     Sched s;
-    s.n_mt = (n + TM - 1) / TM; s.n_nt = (M + TN - 1) / TN; s.nkb = nkb;
+    s.n_mt = (n + tile_tokens - 1) / tile_tokens; s.n_nt = (M + TN - 1) / TN; s.nkb = nkb;
     const int tiles = s.n_mt * s.n_nt;
     s.whole = tiles / grid * grid;
     s.rest = tiles - s.whole;
@@ -186,17 +189,24 @@ template <> struct OutPack<__half> {
     }
 };
 
-template <typename OT, bool TF32, int TN>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x,
+// MT = 128-token blocks per tile (1 or 2). With MT = 2 a tile is 256 tokens x 256 weight rows: two MMAs per k-step share
+// one weight tile (a third less shared-memory fill per flop, which is what bounds the kernel at long prompts); the two
+// accumulators then take all 512 tensor-memory columns, so a tile's epilogue is not overlapped with the next main loop.
+template <typename OT, bool TF32, int TN, int MT>
+__global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x,
                                                                 const __grid_constant__ CUtensorMap tm_x2,
                                                                 const __grid_constant__ CUtensorMap tm_w, OT* __restrict__ C, int64_t ldc,
                                                                 int n, int Mrows, int K, int round_out, float* __restrict__ part, int* err) {
     constexpr int BKE = TF32 ? BK / 2 : BK;                      // K columns of a stage (128 bytes either way)
     constexpr int NX = TF32 ? 2 : 1;                             // activation tiles per stage (hi, lo)
     constexpr uint32_t W_BYTES = TN * 128;
-    constexpr size_t kSlabFloats = (size_t)TM * TN;              // one partial tile
-    constexpr uint32_t STAGE_BYTES = NX * X_BYTES + W_BYTES;
-    constexpr int kStages = kRingBytes / STAGE_BYTES;            // TN 256: 4 (f16), 3 (tf32); TN 128: 6, 4
+    static_assert(MT == 1 || (!TF32 && TN == 256), "256-token tiles: f16, 256 weight rows");
+    constexpr int TT = TM * MT;                                  // tokens per tile
+    constexpr size_t kSlabFloats = (size_t)TT * TN;              // one partial tile
+    constexpr uint32_t XS_BYTES = NX * MT * X_BYTES;             // activation part of a stage
+    constexpr uint32_t STAGE_BYTES = XS_BYTES + W_BYTES;
+    constexpr int kStages = kRingBytes / STAGE_BYTES;            // TN 256: 4 (f16), 3 (tf32, and f16 with MT 2); TN 128: 6, 4
+    constexpr int NACC = MT == 1 ? 2 : 1;                        // accumulator sets in tensor memory
     constexpr uint32_t TMEM_COLS = 2 * TN;
 
     extern __shared__ unsigned char smem_raw[];
@@ -211,7 +221,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (K + BKE - 1) / BKE;
-    const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x, TN);
+    const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x, TN, TT);
 
     if (threadIdx.x == 0) {
         dead_flag = 0;
@@ -221,7 +231,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);
+            mbar_init(&acc_empty[b], 4 * MT);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -235,24 +245,48 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
+    rlb_pdl_trigger();
+    if (!(warp == 0 && lane == 0)) rlb_pdl_wait();  // (the producer thread waits after its weight prefetch)
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer: runs ahead of the MMAs across pieces ----------------
         PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
         Piece p;
-        uint32_t cnt = 0;
-        bool ok = true;
-        while (ok && it.next(p)) {
+        bool have = it.next(p);
+        int kb = have ? p.kb0 : 0;
+        auto advance = [&]() {
+            if (++kb >= p.kb1) { have = it.next(p); kb = have ? p.kb0 : 0; }
+        };
+        // Weights do not depend on earlier kernels: the weight tiles of the first ring stages are requested BEFORE
+        // the wait for the previous kernel (programmatic dependent launch), the activation tiles after it.
+        int npre = 0, pre_kb[8], pre_mt[8];
+        while (have && npre < kStages) {
             const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
-            for (int kb = p.kb0; kb < p.kb1; kb++, cnt++) {
-                const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
-                if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) { ok = false; break; }
-                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                tma_load_2d(st, &tm_x, kb * BKE, mt * TM, &full_bar[s]);
-                if (TF32) tma_load_2d(st + X_BYTES, &tm_x2, kb * BKE, mt * TM, &full_bar[s]);
-                tma_load_2d(st + NX * X_BYTES, &tm_w, kb * BKE, nt * TN, &full_bar[s]);
-            }
+            unsigned char* st = tiles + (size_t)npre * STAGE_BYTES;
+            mbar_expect_tx(&full_bar[npre], STAGE_BYTES);
+            tma_load_2d(st + XS_BYTES, &tm_w, kb * BKE, nt * TN, &full_bar[npre]);
+            pre_kb[npre] = kb; pre_mt[npre] = mt;
+            npre++;
+            advance();
+        }
+        rlb_pdl_wait();
+        for (int i = 0; i < npre; i++) {
+            unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
+            tma_load_2d(st, &tm_x, pre_kb[i] * BKE, pre_mt[i] * TT, &full_bar[i]);   // (one box of TT rows)
+            if (TF32) tma_load_2d(st + X_BYTES, &tm_x2, pre_kb[i] * BKE, pre_mt[i] * TT, &full_bar[i]);
+        }
+        uint32_t cnt = (uint32_t)npre;
+        while (have) {
+            const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
+            const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
+            unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(st, &tm_x, kb * BKE, mt * TT, &full_bar[s]);
+            if (TF32) tma_load_2d(st + X_BYTES, &tm_x2, kb * BKE, mt * TT, &full_bar[s]);
+            tma_load_2d(st + XS_BYTES, &tm_w, kb * BKE, nt * TN, &full_bar[s]);
+            cnt++;
+            advance();
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
@@ -264,8 +298,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         uint32_t cnt = 0, piece = 0;
         bool ok = true;
         while (ok && it.next(p)) {
-            const uint32_t b = piece & 1u;
-            ok = mbar_wait(&acc_empty[b], ((piece >> 1) & 1u) ^ 1u, dead, err);  // the epilogue has drained this accumulator
+            const uint32_t b = NACC == 2 ? (piece & 1u) : 0u;
+            const uint32_t use = NACC == 2 ? (piece >> 1) : piece;  // how often this accumulator set has been used before
+            ok = mbar_wait(&acc_empty[b], (use & 1u) ^ 1u, dead, err);  // the epilogue has drained this accumulator
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t d = tmem_base + b * TN;
@@ -275,42 +310,42 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t x_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                const uint32_t w_addr = x_addr + NX * X_BYTES;
+                const uint32_t w_addr = x_addr + XS_BYTES;
 #pragma unroll
-                for (int pass = 0; pass < NX; pass++)
+                for (int pass = 0; pass < NX * MT; pass++)   // the hi / lo halves (tf32), or the two 128-token blocks (MT = 2)
 #pragma unroll
                     for (int k = 0; k < 4; k++)
                         // one instruction covers 32 bytes of K (16 f16 or 8 tf32 columns) along the swizzled row
-                        umma<TF32>(d, umma_desc(x_addr + pass * X_BYTES + k * 32), umma_desc(w_addr + k * 32), idesc,
-                                   (kb != p.kb0 || pass != 0 || k != 0) ? 1u : 0u);
+                        umma<TF32>(d + (MT == 2 ? pass * TN : 0), umma_desc(x_addr + pass * X_BYTES + k * 32), umma_desc(w_addr + k * 32), idesc,
+                                   (kb != p.kb0 || (MT == 1 && pass != 0) || k != 0) ? 1u : 0u);
                 umma_commit(&empty_bar[s]);  // the slot is free once these MMAs have read it
             }
             if (ok) umma_commit(&acc_full[b]);
             piece++;
         }
     } else if (warp >= 2) {
-        // ---------------- epilogue: warps 2..5, one TMEM lane quarter (32 tokens) each ----------------
-        const int q = warp & 3;
+        // ---------------- epilogue: four warps per 128-token block, one TMEM lane quarter (32 tokens) each ----------------
+        const int q = warp & 3, half = (warp - 2) >> 2;
         PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
         Piece p;
         uint32_t piece = 0;
         const bool vec_c = ((ldc * (int64_t)sizeof(OT)) % 16 == 0) && (((uintptr_t)C & 15) == 0);
         while (it.next(p)) {
-            const uint32_t b = piece & 1u;
-            const bool ok = mbar_wait(&acc_full[b], (piece >> 1) & 1u, dead, err);
+            const uint32_t b = NACC == 2 ? (piece & 1u) : 0u;
+            const bool ok = mbar_wait(&acc_full[b], (NACC == 2 ? (piece >> 1) : piece) & 1u, dead, err);
             __syncwarp();
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
-            const int token = mt * TM + q * 32 + lane;
+            const int token = mt * TT + half * TM + q * 32 + lane;
             const int col_base = nt * TN;
-            float* slab = p.slot >= 0 ? part + ((size_t)blockIdx.x * 2 + p.slot) * kSlabFloats + (size_t)(q * 32 + lane) * TN : nullptr;
+            float* slab = p.slot >= 0 ? part + ((size_t)blockIdx.x * 2 + p.slot) * kSlabFloats + (size_t)(half * TM + q * 32 + lane) * TN : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < TN; c0 += 32) {
                 if (col_base + c0 >= Mrows) break;  // (uniform over the warp)
                 // two loads of 16 columns in flight before the wait
                 uint32_t r[2][16];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + b * TN + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (b + (uint32_t)half) * TN + (uint32_t)c0;
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                     asm volatile(
@@ -352,15 +387,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
 }
 
 // Second pass for the tiles that were dealt out by k-block: out = cast(round?(sum of the tile's partial tiles
-// in k order)). grid (remaining tiles, TM / 8 groups of 8 token rows). The CTAs whose runs meet the tile are
+// in k order)). grid (remaining tiles, groups of 8 token rows). The CTAs whose runs meet the tile are
 // found by all threads at once (thread c looks at CTA c); they are consecutive, and their order is the k order.
-template <typename OT, int TN>
+template <typename OT, int TN, int MT>
 __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ part, OT* __restrict__ C, int64_t ldc, int n, int Mrows,
                                                             int nkb, int grid, int round_out) {
-    constexpr size_t kSlabFloats = (size_t)TM * TN;
+    constexpr int TT = TM * MT;
+    constexpr size_t kSlabFloats = (size_t)TT * TN;
     __shared__ int seg_slab[kMaxGrid];   // slab index (cta * 2 + slot) of CTA c's piece of this tile, or -1
     __shared__ int c_lo_s, c_hi_s;
-    const Sched s = make_sched(n, Mrows, nkb, grid, TN);
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
+    const Sched s = make_sched(n, Mrows, nkb, grid, TN, TT);
     const int j = blockIdx.x;
     const long long u_first = (long long)j * s.nkb, u_last = u_first + s.nkb;
     if (threadIdx.x == 0) { c_lo_s = grid; c_hi_s = -1; }
@@ -384,7 +422,7 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     const bool vec_c = ((ldc * (int64_t)sizeof(OT)) % 16 == 0) && (((uintptr_t)C & 15) == 0);
     for (int e = threadIdx.x; e < 8 * (TN / 4); e += 256) {
         const int rr = row0 + e / (TN / 4), c4 = (e % (TN / 4)) * 4;
-        const int token = mt * TM + rr, col = nt * TN + c4;
+        const int token = mt * TT + rr, col = nt * TN + c4;
         if (token >= n || col >= Mrows) continue;
         const float* src = part + (size_t)rr * TN + c4;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -468,6 +506,8 @@ int reserve_scratch(rlb_ctx* ctx, size_t need) {
 
 // hi = x rounded to TF32 (10 explicit mantissa bits), lo = x - hi (exact in f32)
 __global__ void tf32_split_kernel(const float* __restrict__ x, int64_t ldx, int n, int K, float* __restrict__ hi, float* __restrict__ lo) {
+    rlb_pdl_trigger();
+    rlb_pdl_wait();
     const int64_t total = (int64_t)n * K;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / K, c = i - r * K;
@@ -480,16 +520,17 @@ __global__ void tf32_split_kernel(const float* __restrict__ x, int64_t ldx, int 
     }
 }
 
-template <typename OT, bool TF32, int TN>
+template <typename OT, bool TF32, int TN, int MT>
 int launch_tn(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
               int* err) {
     constexpr int BKE = TF32 ? BK / 2 : BK;
-    constexpr size_t kSlabFloats = (size_t)TM * TN;
+    constexpr int TT = TM * MT;
+    constexpr size_t kSlabFloats = (size_t)TT * TN;
     const int nkb = (K + BKE - 1) / BKE;
-    const long long units = (long long)((n + TM - 1) / TM) * ((M + TN - 1) / TN) * nkb;
+    const long long units = (long long)((n + TT - 1) / TT) * ((M + TN - 1) / TN) * nkb;
     const int max_grid = ctx->sm_count < kMaxGrid ? ctx->sm_count : kMaxGrid;
     const int grid = (int)(units < max_grid ? units : max_grid);
-    const Sched sched = make_sched(n, M, nkb, grid, TN);
+    const Sched sched = make_sched(n, M, nkb, grid, TN, TT);
     // scratch: [x hi | x lo] for the f32 form, then two partial tiles per CTA (only touched when tiles are dealt out by k-block)
     const size_t xs = TF32 ? (((size_t)n * K * sizeof(float) + 255) & ~(size_t)255) : 0;
     const size_t slabs = sched.rest > 0 ? (size_t)grid * 2 * kSlabFloats * sizeof(float) : 0;
@@ -503,28 +544,26 @@ int launch_tn(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
         const int64_t total = (int64_t)n * K;
         int g = (int)((total + 255) / 256);
         if (g > ctx->sm_count * 16) g = ctx->sm_count * 16;
-        tf32_split_kernel<<<g, 256, 0, ctx->stream>>>(static_cast<const float*>(X), ldx, n, K, hi, lo);
-        RLB_LAUNCH_CHECK();
+        RLB_CUDA(rlb_launch(tf32_split_kernel, dim3(g), dim3(256), 0, ctx, static_cast<const float*>(X), ldx, n, K, hi, lo));
         count_launch(ctx);
         RLB_TRY(make_map(&tx, hi, n, K, K, TM, true));
         RLB_TRY(make_map(&tx2, lo, n, K, K, TM, true));
     } else {
-        RLB_TRY(make_map(&tx, X, n, K, ldx, TM));
+        RLB_TRY(make_map(&tx, X, n, K, ldx, TT));
         tx2 = tx;
     }
     const size_t smem = (size_t)kRingBytes + 1024;
-    auto kern = gemm_tc_kernel<OT, TF32, TN>;
+    auto kern = gemm_tc_kernel<OT, TF32, TN, MT>;
     static std::atomic<uint64_t> set{0};
     if (!attr_done(set, ctx->device)) {
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_mark(set, ctx->device);
     }
-    kern<<<grid, kTcThreads, smem, ctx->stream>>>(tx, tx2, tw, C, ldc, n, M, K, round_out, part, err);
-    RLB_LAUNCH_CHECK();
+    RLB_CUDA(rlb_launch(kern, dim3(grid), dim3(tc_threads(MT)), smem, ctx, tx, tx2, tw, C, ldc, n, M, K, round_out, part, err));
     count_launch(ctx);
     if (sched.rest > 0) {
-        gemm_tc_fixup_kernel<OT, TN><<<dim3(sched.rest, TM / 8), 256, 0, ctx->stream>>>(part, C, ldc, n, M, nkb, grid, round_out);
-        RLB_LAUNCH_CHECK();
+        RLB_CUDA(rlb_launch(gemm_tc_fixup_kernel<OT, TN, MT>, dim3(sched.rest, TT / 8), dim3(256), 0, ctx, (const float*)part, C, ldc, n, M, nkb, grid,
+                            round_out));
         count_launch(ctx);
     }
     return RLB_OK;
@@ -537,8 +576,16 @@ int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
     // 256-row tiles where whole tiles can be handed out; 128-row tiles when there are fewer tiles than SMs, where
     // every tile is split over K anyway and the narrower tile halves the partial results
     const long long tiles256 = (long long)((n + TM - 1) / TM) * ((M + 255) / 256);
-    if (tiles256 < ctx->sm_count) return launch_tn<OT, TF32, 128>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
-    return launch_tn<OT, TF32, 256>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    static const int force_tn = getenv("RLB_GEMM_TN") ? atoi(getenv("RLB_GEMM_TN")) : 0;  // experiments: 128, 256 or 512 (= 256-token tiles)
+    if (!TF32) {
+        // 256-token tiles when there are enough of them to hand out whole tiles to every SM
+        const long long tiles_big = (long long)((n + 2 * TM - 1) / (2 * TM)) * ((M + 255) / 256);
+        if (force_tn == 512 || (force_tn == 0 && n > TM && tiles_big >= ctx->sm_count))
+            return launch_tn<OT, false, 256, 2>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    }
+    if (force_tn == 256) return launch_tn<OT, TF32, 256, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    if (force_tn == 128 || tiles256 < ctx->sm_count) return launch_tn<OT, TF32, 128, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    return launch_tn<OT, TF32, 256, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
 }
 
 }  // namespace

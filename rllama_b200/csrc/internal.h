@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/rllama_b200.h"
@@ -51,6 +52,10 @@ struct rlb_ctx {
     // synchronisation without a copy (raised when a bounded device-side wait ran out)
     int* h_err = nullptr;
     int* d_err = nullptr;
+    // set while the model's prefill enqueues its kernels: they are then launched as programmatic dependents
+    // (each may start while its predecessor drains; every one of them waits for the predecessor before it
+    // touches anything but weights)
+    bool pdl_chain = false;
 };
 int ctx_check_error_word(rlb_ctx* ctx);  // after a synchronisation: RLB_ERR_CUDA if a kernel raised the word
 
@@ -238,6 +243,27 @@ int launch_gemm_tc_f16out(rlb_ctx* ctx, const void* X, int64_t ldx, const void* 
 // ---------------------------------------------------------------------------------------
 // helpers
 // ---------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+// Programmatic dependent launch: rlb_pdl_trigger lets the next kernel of the stream start launching now;
+// rlb_pdl_wait blocks until the previous kernel has completed and its writes are visible. Both are no-ops in a
+// kernel launched the ordinary way. A kernel launched through rlb_launch must execute the wait in every CTA
+// before it reads or writes anything an earlier kernel touches.
+__device__ __forceinline__ void rlb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void rlb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Kernel launch on the context's stream; as a programmatic dependent while ctx->pdl_chain is set.
+template <typename... KA, typename... A>
+inline cudaError_t rlb_launch(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, rlb_ctx* ctx, A&&... args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = ctx->pdl_chain ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, kern, std::forward<A>(args)...);
+}
+#endif
 static inline void count_launch(rlb_ctx* ctx, uint64_t n = 1) { ctx->launches += n; }
 // Function attributes (shared-memory opt-in) are per device: a call site keeps one bit per device index in
 // `mask`, tests it with attr_done and sets it with attr_mark once cudaFuncSetAttribute has succeeded there.

@@ -405,6 +405,9 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
     const int d = m->p.dim, nq = m->nq, F = m->F;
     const bool f16 = m->wdt == RLB_F16;
     const int round_proj = (f16 && m->tp == 1) ? 1 : 0;  // with tensor parallelism the rounding follows the reduction
+    // the kernels of this chain are launched as programmatic dependents of one another (see rlb_launch)
+    struct ChainGuard { rlb_ctx* c; ~ChainGuard() { c->pdl_chain = false; } } chain_guard{ctx};
+    ctx->pdl_chain = m->use_pdl && n <= 512;  // (beyond that the kernels run for hundreds of microseconds and nothing is gained)
     RLB_TRY(launch_embed(ctx, m->tok_emb, m->pf_tokens, n, d, m->pf_x));
 
     // The residual add of a projection's output (src/transformer.rs:442-445) is folded into the RMSNorm that follows
@@ -442,7 +445,11 @@ int enqueue_prefill(rlb_model* m, rlb_caches* c, int n, int start_pos) {
     GemvArgs a;
     a.W = m->output; a.rows = m->V; a.K = d; a.ldw = d; a.vec_in = m->pf_last;
     a.out = m->tp == 1 ? m->logits : m->logits_local;
-    RLB_TRY(launch_gemv(ctx, RLB_F32, PRO_COPY, EPI_F32, a));
+    {   // the staged GEMV where it takes the shape (the head is the largest single matrix), else the register-staged one
+        int s = m->use_stream ? launch_gemv_stream(ctx, RLB_F32, PRO_COPY, EPI_F32, a, m->scalars + 8, 0) : RLB_ERR_STATE;
+        if (s == RLB_ERR_STATE) s = launch_gemv(ctx, RLB_F32, PRO_COPY, EPI_F32, a);
+        RLB_TRY(s);
+    }
     if (m->tp > 1) RLB_TRY(nccl_allgather_f32(&m->nccl, m->logits_local, m->logits, (size_t)m->V, ctx->stream));
     return RLB_OK;
 }

@@ -51,6 +51,20 @@ def test_matrix_mul_transposed_1024_square(cuda_ctx):
     assert rel_close(got, want, 1e-1)
 
 
+@pytest.mark.parametrize("n,M,K", [(300, 40000, 1024), (640, 38000, 520), (129, 40000, 256)])
+def test_matrix_mul_transposed_many_tiles(cuda_ctx, n, M, K):
+    """Enough output tiles for every schedule of the tensor-core GEMM: whole 256-token x 256-row tiles handed
+    out round-robin plus a K-split remainder, a partial last token tile, a partial last row tile, a K that is not
+    a multiple of the 64-column k-block."""
+    rng = np.random.default_rng(9)
+    x = rng.uniform(-1, 1, (n, K)).astype(np.float16); w = rng.uniform(-1, 1, (M, K)).astype(np.float16)
+    want = O.matrix_mul_transposed(x, w, nthreads=8).astype(np.float32)
+    got = gpu_mmt(cuda_ctx, x, w).astype(np.float32)
+    assert got.shape == want.shape
+    assert rel_close(got, want, 1e-2, f16_ulps=1)
+    assert (got == want).mean() > 0.97  # same f32 sums up to order, one f16 rounding
+
+
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
 def test_matrix_mul_transposed_random_sizes(cuda_ctx, dtype):
     # src/tensor.rs:2986-3090: sizes up to 300, including one row on either side; 1e-2
