@@ -403,6 +403,7 @@ template <> __device__ __forceinline__ void row_unpack<float, 2>(const uint2& v,
 }
 
 constexpr int kFastMinChunk = 64;  // positions per CTA at least (a multiple of kWarps)
+constexpr int kMaxCluster = 16;    // splits of a head that may form one thread-block cluster (beyond 8: non-portable size)
 
 __host__ __device__ inline int fast_chunk(int T, int ns) {
     int chunk = (T + ns - 1) / ns;
@@ -427,10 +428,11 @@ __device__ __forceinline__ void cluster_sync() {
 // CTA that draws the last ticket merges them. CL = true: the n_split (<= 8) CTAs of a head form a
 // thread-block cluster, send their partial result into the shared memory of the cluster's first
 // CTA and meet at the cluster barrier: no global round trips on the way to the merged row.
-template <typename CT, int HD, bool CL>
+// PB = positions per warp per batch (8 or 16): a CTA requests 8 PB cache rows of K and of V at once, and the
+// first batch before the dependency wait; 16 is chosen when a CTA may own more than 64 positions (long contexts).
+template <typename CT, int HD, bool CL, int PB>
 __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDecodeArgs a) {
     constexpr int DPL = HD / 32;
-    constexpr int PB = 8;  // positions per warp per batch
     typedef typename RowVec<CT, DPL>::T RV;
     __shared__ float w_m[kWarps], w_l[kWarps];
     __shared__ float w_o[kWarps][HD];
@@ -534,8 +536,8 @@ __global__ void __launch_bounds__(kThreads) attn_decode_fast_kernel(const AttnDe
         for (int w = 0; w < kWarps; w++) o += w_o[w][c] * expf(w_m[w] - M);
     }
     if constexpr (CL) {
-        __shared__ float r_o[8][HD];
-        __shared__ float r_m[8], r_l[8];
+        __shared__ float r_o[kMaxCluster][HD];
+        __shared__ float r_m[kMaxCluster], r_l[kMaxCluster];
         asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster has started
         if (work) {
             if (c < HD) cluster_store(cluster_map(&r_o[split][c], 0), o);
@@ -632,8 +634,8 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
     static const bool use_cluster = getenv("RLB_ATTN_CLUSTER") == nullptr || atoi(getenv("RLB_ATTN_CLUSTER")) != 0;
     if (use_fast && (a.hd == 64 || a.hd == 128)) {
         lc.dynamicSmemBytes = 0;
-        // the splits of a head as one thread-block cluster (portable cluster sizes end at 8)
-        const bool cluster = use_cluster && a.n_split <= 8;
+        // the splits of a head as one thread-block cluster (sizes beyond 8 are non-portable and need an opt-in)
+        const bool cluster = use_cluster && a.n_split <= kMaxCluster;
         if (cluster) {
             cudaLaunchAttribute& ca = attr[lc.numAttrs++];
             ca.id = cudaLaunchAttributeClusterDimension;
@@ -641,14 +643,19 @@ int launch_attn_decode(rlb_ctx* ctx, rlb_dtype cache_dtype, const AttnDecodeArgs
             ca.val.clusterDim.y = (unsigned)a.n_split;
             ca.val.clusterDim.z = 1;
         }
+        // A CTA that may own more than 128 positions takes 16 per warp and batch -- but only while the grid is at most one
+        // CTA per SM (few local heads, i.e. tensor parallelism). Measured on 8 local heads at context 1800: 8 splits 33.4 us
+        // per layer, 8 splits with 16 per batch 31.0, 16 splits 30.2, 16 splits with 16 per batch 32.6 (the larger register
+        // footprint costs more than the shorter chain of batches saves; 65B on one GPU: 22.0 -> 23.5 ms/token with it).
+        static const int wide_env = getenv("RLB_ATTN_WIDE") ? atoi(getenv("RLB_ATTN_WIDE")) : -1;  // experiments: force off / on
+        const bool wide = wide_env >= 0 ? wide_env != 0 : (fast_chunk(a.max_seq, a.n_split) > 128 && a.heads * a.n_split <= ctx->sm_count);
         const void* kern;
-        if (cache_dtype == RLB_F16) {
-            if (a.hd == 128) kern = cluster ? (const void*)attn_decode_fast_kernel<__half, 128, true> : (const void*)attn_decode_fast_kernel<__half, 128, false>;
-            else kern = cluster ? (const void*)attn_decode_fast_kernel<__half, 64, true> : (const void*)attn_decode_fast_kernel<__half, 64, false>;
-        } else {
-            if (a.hd == 128) kern = cluster ? (const void*)attn_decode_fast_kernel<float, 128, true> : (const void*)attn_decode_fast_kernel<float, 128, false>;
-            else kern = cluster ? (const void*)attn_decode_fast_kernel<float, 64, true> : (const void*)attn_decode_fast_kernel<float, 64, false>;
-        }
+#define RLB_ATTN_PICK(CT, HD) (cluster ? (wide ? (const void*)attn_decode_fast_kernel<CT, HD, true, 16> : (const void*)attn_decode_fast_kernel<CT, HD, true, 8>) \
+                                       : (wide ? (const void*)attn_decode_fast_kernel<CT, HD, false, 16> : (const void*)attn_decode_fast_kernel<CT, HD, false, 8>))
+        if (cache_dtype == RLB_F16) kern = a.hd == 128 ? RLB_ATTN_PICK(__half, 128) : RLB_ATTN_PICK(__half, 64);
+        else kern = a.hd == 128 ? RLB_ATTN_PICK(float, 128) : RLB_ATTN_PICK(float, 64);
+#undef RLB_ATTN_PICK
+        if (cluster && a.n_split > 8) RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         // same shared-memory split as the projection kernels before and after this one, so that their
         // CTAs (which prefetch weights while they wait for this kernel) can share an SM with these
         RLB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));

@@ -573,8 +573,8 @@ int rlb_model_create(rlb_ctx* ctx, const rlb_model_params* p, rlb_model** out) {
     const int max_ns = (p->max_seq_len + 63) / 64;
     if (ns > max_ns) ns = max_ns;
     if (ns > 32) ns = 32;
-    // up to 8 splits run as one thread-block cluster per head and merge through distributed shared memory
-    if (ns > 8 && (getenv("RLB_ATTN_CLUSTER") == nullptr || atoi(getenv("RLB_ATTN_CLUSTER")) != 0)) ns = 8;
+    // up to 16 splits run as one thread-block cluster per head and merge through distributed shared memory
+    if (ns > 16 && (getenv("RLB_ATTN_CLUSTER") == nullptr || atoi(getenv("RLB_ATTN_CLUSTER")) != 0)) ns = 16;
     if (ns < 1) ns = 1;
     if (const char* e = getenv("RLB_ATTN_SPLIT")) { int v = atoi(e); if (v >= 1 && v <= 64) ns = v; }
     m->n_split = ns;

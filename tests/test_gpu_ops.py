@@ -151,7 +151,7 @@ def attention_case(rng, heads, hd, max_seq, dtype):
 def test_attention_decode_op(cuda_ctx, dtype):
     rng = np.random.default_rng(5)
     for heads, hd, max_seq, pos, n_split in [(4, 64, 96, 70, 1), (4, 64, 96, 70, 4), (3, 128, 300, 299, 5), (2, 128, 64, 0, 2),
-                                             (8, 128, 2048, 2047, 16)]:
+                                             (8, 128, 2048, 2047, 16), (8, 128, 2048, 2047, 24), (5, 64, 1536, 1400, 12)]:
         q, k, v = attention_case(rng, heads, hd, max_seq, dtype)
         tq, tk, tv = cuda_ctx.upload(q), cuda_ctx.upload(k), cuda_ctx.upload(v)
         out = cuda_ctx.zeros(1, heads * hd, F16 if dtype == np.float16 else F32)

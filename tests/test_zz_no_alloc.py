@@ -7,7 +7,7 @@ ABI several times in a row -- the array keeps the previous call's contents, so e
 call checks that what must start at zero is cleared and that stale records are not read --
 and compares each result with the allocating entry point ``rlb_attention_decode`` on the same
 inputs and with a float64 statement of the attention itself. The shapes are chosen so that the
-fixed array is really used: more than eight splits (the splits of a head then meet through
+fixed array is really used: more than sixteen splits (the splits of a head then meet through
 records and an arrival counter in the array, not through a cluster's shared memory) and a
 head dimension that takes the general kernel. This file sorts last so that a run stopping at
 the first failure has already run every other test.
@@ -48,11 +48,11 @@ def run_both(ctx, rng, heads, hd, max_seq, pos, n_split, dtype):
 
 
 # (heads, head_dim, max_seq, pos, n_split). The first three take the path through the fixed array's
-# records and counters (16 or 12 splits of 64 positions or more); the fourth the general kernel
-# (head_dim 192), also through the records; the last three the cluster path, which only needs the
-# array to be left alone.
-CASES = [(8, 128, 2048, 2047, 16), (8, 128, 2048, 2047, 16), (6, 64, 1024, 1000, 12), (3, 192, 300, 299, 5),
-         (8, 128, 512, 500, 8), (4, 64, 96, 70, 3), (8, 128, 512, 37, 8)]
+# records and counters (24 or 20 splits of 64 positions or more; up to 16 splits would form a cluster);
+# the fourth the general kernel (head_dim 192), also through the records; the last four the cluster
+# path (16 splits included), which only needs the array to be left alone.
+CASES = [(8, 128, 2048, 2047, 24), (8, 128, 2048, 2047, 24), (6, 64, 2048, 2000, 20), (3, 192, 300, 299, 5),
+         (8, 128, 2048, 2047, 16), (8, 128, 512, 500, 8), (4, 64, 96, 70, 3), (8, 128, 512, 37, 8)]
 
 
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
