@@ -42,7 +42,7 @@ constexpr int TK = 128;           // cache positions per tile
 constexpr int kSoftmaxWarps = 8;
 constexpr int kThreadsTc = (kSoftmaxWarps + 2) * 32;  // + TMA warp + MMA warp
 constexpr uint32_t kWaitLimit = 1u << 22;
-constexpr float kPScale = 16384.f;  // 2^14
+constexpr float kPShift = 14.f;     // the softmax weights carry a factor 2^14 (see the file comment)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -119,17 +119,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxWarps * 32) : "memory"); }
 
-// x = hi + lo in f16 halves, eight values packed for one 16-byte shared-memory store each.
+// x = hi + lo in f16 halves, eight values packed for one 16-byte shared-memory store each (packed conversions:
+// two values per instruction).
 __device__ __forceinline__ void split8(const float (&x)[8], uint4& hi, uint4& lo) {
     uint32_t h[4], l[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const __half h0 = __float2half_rn(x[2 * i]), h1 = __float2half_rn(x[2 * i + 1]);
-        const __half l0 = __float2half_rn(x[2 * i] - __half2float(h0)), l1 = __float2half_rn(x[2 * i + 1] - __half2float(h1));
-        h[i] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-        l[i] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        const __half2 hh = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+        const float2 hf = __half22float2(hh);
+        const __half2 ll = __floats2half2_rn(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
+        h[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        l[i] = *reinterpret_cast<const uint32_t*>(&ll);
     }
     hi = make_uint4(h[0], h[1], h[2], h[3]);
     lo = make_uint4(l[0], l[1], l[2], l[3]);
@@ -300,7 +307,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
         const int quarter = warp & 3, half = warp >> 2;      // TMEM lane quarter, column half
         const int r = quarter * 32 + lane;                   // row of the query block
         const int limit = a.start_pos + i0 + r + 1;          // attends to positions below this (src/tensor.rs:496-508)
-        const float scale = 1.0f / sqrtf((float)HD);         // src/transformer.rs:770
+        // 1 / sqrt(head_dim) (src/transformer.rs:770) times log2(e): the softmax is evaluated with 2^x (ex2.approx, relative
+        // error below 2^-22, the precision of the two-half split); softmax(s) = 2^(s c - m) / sum with c = log2(e)
+        const float scale2 = (1.0f / sqrtf((float)HD)) * 1.4426950408889634f;
         constexpr int OC = HD / 2;                           // output columns of this thread
         float o[OC];
 #pragma unroll
@@ -318,12 +327,13 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
             float p[64];
             const uint32_t s_addr = tmem_base + lane_addr + (sb ? S_COL1 : S_COL0) + (uint32_t)half * 64;
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(s_addr + c0, v);
+            for (int c0 = 0; c0 < 64; c0 += 32) {   // two loads of 16 columns in flight per wait
+                uint32_t v[2][16];
+                tmem_ld16(s_addr + c0, v[0]);
+                tmem_ld16(s_addr + c0 + 16, v[1]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 16; e++) p[c0 + e] = __uint_as_float(v[e]);
+                for (int e = 0; e < 16; e++) { p[c0 + e] = __uint_as_float(v[0][e]); p[c0 + 16 + e] = __uint_as_float(v[1][e]); }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -332,19 +342,21 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
             float tmax = -FLT_MAX;
 #pragma unroll
             for (int e = 0; e < 64; e++) {
-                p[e] = (t_first + e < limit) ? p[e] * scale : -FLT_MAX;   // the causal mask
+                p[e] = (t_first + e < limit) ? p[e] * scale2 : -FLT_MAX;   // the causal mask; scores in units of log2(e)
                 tmax = fmaxf(tmax, p[e]);
             }
             xmax[sb][half][r] = tmax;
             softmax_sync();
             const float m_new = fmaxf(m_run, fmaxf(tmax, xmax[sb][half ^ 1][r]));
-            const float alpha = expf(m_run - m_new);
+            const float alpha = ex2_approx(m_run - m_new);
+            // weights as 2^(s - m + 14): the factor 2^14 keeps the low f16 half normal and cancels in o / l at the end
+            const float shift = kPShift - m_new;
             float psum = 0.f;
 #pragma unroll
             for (int e = 0; e < 64; e++) {
-                const float pv = (t_first + e < limit) ? expf(p[e] - m_new) : 0.f;
+                const float pv = (t_first + e < limit) ? ex2_approx(p[e] + shift) : 0.f;
                 psum += pv;
-                p[e] = pv * kPScale;
+                p[e] = pv;
             }
             l_run = l_run * alpha + psum;
             m_run = m_new;
@@ -355,12 +367,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t o_addr = tmem_base + lane_addr + O_COL + (uint32_t)half * OC;
 #pragma unroll
-                for (int c0 = 0; c0 < OC; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(o_addr + c0, v);
+                for (int c0 = 0; c0 < OC; c0 += 32) {
+                    uint32_t v[2][16];
+                    tmem_ld16(o_addr + c0, v[0]);
+                    tmem_ld16(o_addr + c0 + 16, v[1]);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 16; e++) o[c0 + e] = fmaf(o[c0 + e], alpha_prev, __uint_as_float(v[e]));
+                    for (int e = 0; e < 16; e++) {
+                        o[c0 + e] = fmaf(o[c0 + e], alpha_prev, __uint_as_float(v[0][e]));
+                        o[c0 + 16 + e] = fmaf(o[c0 + 16 + e], alpha_prev, __uint_as_float(v[1][e]));
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
@@ -387,12 +403,16 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t o_addr = tmem_base + lane_addr + O_COL + (uint32_t)half * OC;
 #pragma unroll
-                for (int c0 = 0; c0 < OC; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(o_addr + c0, v);
+                for (int c0 = 0; c0 < OC; c0 += 32) {
+                    uint32_t v[2][16];
+                    tmem_ld16(o_addr + c0, v[0]);
+                    tmem_ld16(o_addr + c0 + 16, v[1]);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 16; e++) o[c0 + e] = fmaf(o[c0 + e], alpha_prev, __uint_as_float(v[e]));
+                    for (int e = 0; e < 16; e++) {
+                        o[c0 + e] = fmaf(o[c0 + e], alpha_prev, __uint_as_float(v[0][e]));
+                        o[c0 + 16 + e] = fmaf(o[c0 + 16 + e], alpha_prev, __uint_as_float(v[1][e]));
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
@@ -401,7 +421,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) attn_prefill_tc_kernel(const __
         xsum[half][r] = l_run;
         softmax_sync();
         if (ok && r < rows) {
-            const float inv = 1.0f / ((xsum[0][r] + xsum[1][r]) * kPScale);
+            const float inv = 1.0f / (xsum[0][r] + xsum[1][r]);  // (numerator and denominator both carry 2^14)
             __half* dst = a.out + (int64_t)(i0 + r) * a.heads * HD + head * HD + half * OC;
 #pragma unroll
             for (int c8 = 0; c8 < OC / 8; c8++) {
