@@ -10,9 +10,10 @@
 // x = hi + lo with hi = f16(x) and lo = f16(x - hi), and both halves are multiplied into the same
 // f32 accumulator (tcgen05.mma kind::f16; products of f16 values are exact in f32). Two halves carry
 // 22 significant bits; what is dropped is below 2^-22 of x, or below 2^-25 in absolute terms where
-// the low half falls into f16's subnormal range. p is multiplied by 2^14 before the split (it lies in
-// [0, 1]; the power of two is exact and is taken out again at the end) so that its low half stays a
-// normal number down to p = 2^-17.
+// the low half falls into f16's subnormal range. p carries a factor 2^14 (it lies in [0, 1]; the factor is
+// folded into the exponent of 2^(s - m) and cancels in o / l at the end) so that its low half stays a
+// normal number down to p = 2^-17. The exponential is ex2.approx (relative error below 2^-22) on scores
+// pre-multiplied by log2(e).
 //
 // One CTA owns 128 query rows of one head and walks the cache in tiles of 128 positions:
 //  * one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of the K and V tiles
@@ -25,8 +26,9 @@
 //    reads its scores with tcgen05.ld, keeps the running maximum, sum and output in registers,
 //    writes the split weights to shared memory as the A operand of the output product and adds
 //    the previous tile's O_tile (rescaled) to its output row.
-// Every wait is bounded; when one runs out the kernel raises the error word, every role leaves its
-// loop, and the tensor memory is released before the CTA returns.
+// Every wait is bounded; when one runs out the kernel raises the error word, no later wait of the CTA
+// blocks any more (the softmax warps still run their loop to its end so that every thread keeps meeting
+// their named barrier), and the tensor memory is released before the CTA returns.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 

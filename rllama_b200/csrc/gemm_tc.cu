@@ -18,10 +18,13 @@
 //    timing) and applies the output rounding.
 //  * Operands arrive by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the tensor)
 //    into a 192 KB shared-memory ring; one thread issues the loads and runs ahead across tiles.
-//  * One thread issues tcgen05.mma (kind::f16, M 128, N 256, K 16 per instruction) into one of two
-//    accumulators in tensor memory (2 x 256 columns): the next tile's main loop runs while four warps
+//  * One thread issues tcgen05.mma (kind::f16, M 128, N TN, K 16 per instruction) into one of two
+//    accumulators in tensor memory (2 x TN columns): the next tile's main loop runs while four warps
 //    read the finished accumulator back with tcgen05.ld, round to f16 where the reference rounds the
-//    GEMM result, and store 64 contiguous bytes per thread and step.
+//    GEMM result, and store 64 contiguous bytes per thread and step. Long prompts use 256-token tiles
+//    (template parameter MT = 2, see the kernel): two MMAs per k-step on one weight tile.
+//  * The kernel is a programmatic dependent of its predecessor: the weight tiles of the first ring
+//    stages are requested before the wait for the previous kernel, the activation tiles after it.
 // Products of f16 values are exact in f32; only the summation order differs from the reference's
 // 8-lane FMA scheme.
 //
