@@ -42,14 +42,15 @@
 
 #include <cstdlib>
 
+#include "gemm_sched.h"
 #include "internal.h"
 
 namespace {
 
-constexpr int TM = 128;       // tokens per tile (MMA M)
+constexpr int TM = gemm_sched::TM;   // tokens per MMA block (MMA M)
 // (weight rows per tile, MMA N: template parameter TN, 256 or 128)
 constexpr int BK = 64;        // K columns per stage in f16 (128 bytes = one swizzle span)
-constexpr int kRingBytes = 192 * 1024;
+constexpr int kRingBytes = 192 * 1024;   // stage ring (224 KB gives the 128-row tiles a seventh stage and measured the same)
 // threads: warp 0 TMA, warp 1 MMA, then four epilogue warps per 128-token block of a tile
 constexpr int tc_threads(int mt) { return 64 + 128 * mt; }
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -120,47 +121,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// ---- the schedule --------------------------------------------------------------------------------
-struct Sched {
-    int n_mt, n_nt, nkb;   // token tiles, weight-row tiles, k-blocks per tile
-    int whole;             // tiles handed out whole, round-robin (a multiple of the grid size)
-    int rest;              // remaining tiles, dealt out by k-block
-};
-__host__ __device__ inline Sched make_sched(int n, int M, int nkb, int grid, int TN, int tile_tokens) {
-    Sched s;
-    s.n_mt = (n + tile_tokens - 1) / tile_tokens; s.n_nt = (M + TN - 1) / TN; s.nkb = nkb;
-    const int tiles = s.n_mt * s.n_nt;
-    s.whole = tiles / grid * grid;
-    s.rest = tiles - s.whole;
-    return s;
-}
-// First k-block unit of CTA c's run over the remaining tiles (units are numbered tile-major).
-__host__ __device__ inline long long rest_begin(const Sched& s, int c, int grid) { return (long long)c * s.rest * s.nkb / grid; }
-
-// One piece of work: k-blocks [kb0, kb1) of a tile. `slot` < 0: the piece covers the whole K range and
-// its result goes straight to the output; otherwise it is partial tile number `slot` (0 or 1) of this CTA.
-struct Piece { int tile, kb0, kb1, slot; };
-struct PieceIter {
-    Sched s; int cta, grid;
-    int t;                  // next whole tile
-    long long u, u0, u1;    // position in, and bounds of, this CTA's run over the remaining tiles
-    __device__ PieceIter(const Sched& s_, int cta_, int grid_) : s(s_), cta(cta_), grid(grid_) {
-        t = cta;
-        u0 = rest_begin(s, cta, grid); u1 = rest_begin(s, cta + 1, grid); u = u0;
-    }
-    __device__ bool next(Piece& p) {
-        if (t < s.whole) { p.tile = t; p.kb0 = 0; p.kb1 = s.nkb; p.slot = -1; t += grid; return true; }
-        if (u >= u1) return false;
-        const int j = (int)(u / s.nkb);
-        p.tile = s.whole + j;
-        p.kb0 = (int)(u - (long long)j * s.nkb);
-        const long long left = u1 - u;
-        p.kb1 = (int)(p.kb0 + left < s.nkb ? p.kb0 + left : s.nkb);
-        p.slot = (p.kb0 == 0 && p.kb1 == s.nkb) ? -1 : (u == u0 ? 0 : 1);
-        u += p.kb1 - p.kb0;
-        return true;
-    }
-};
+using gemm_sched::Sched;
+using gemm_sched::make_sched;
+using gemm_sched::rest_begin;
+using gemm_sched::Piece;
+using gemm_sched::PieceIter;
 
 template <typename OT> struct OutPack;
 template <> struct OutPack<float> {
@@ -403,14 +368,11 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     rlb_pdl_wait();
     const Sched s = make_sched(n, Mrows, nkb, grid, TN, TT);
     const int j = blockIdx.x;
-    const long long u_first = (long long)j * s.nkb, u_last = u_first + s.nkb;
     if (threadIdx.x == 0) { c_lo_s = grid; c_hi_s = -1; }
     __syncthreads();
     for (int c = threadIdx.x; c < grid; c += blockDim.x) {
-        const long long b = rest_begin(s, c, grid), e = rest_begin(s, c + 1, grid);
-        int slab = -1;
-        if (e > b && b < u_last && e > u_first) {   // CTA c's run meets the tile
-            slab = c * 2 + (b >= u_first ? 0 : 1);  // the piece starts the run, or follows a tile boundary inside it
+        const int slab = gemm_sched::partial_of(s, grid, j, c);
+        if (slab >= 0) {   // CTA c's run meets the tile
             atomicMin(&c_lo_s, c);
             atomicMax(&c_hi_s, c);
         }
@@ -576,18 +538,26 @@ template <typename OT, bool TF32>
 int launch_tc(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t ldw, OT* C, int64_t ldc, int n, int M, int K, int round_out,
               int* err) {
     RLB_TRY(load_encode());
-    // 256-row tiles where whole tiles can be handed out; 128-row tiles when there are fewer tiles than SMs, where
-    // every tile is split over K anyway and the narrower tile halves the partial results
-    const long long tiles256 = (long long)((n + TM - 1) / TM) * ((M + 255) / 256);
+    // Tile choice, from a sweep over the four models' layer shapes and prompts of 128 to 1792 tokens:
+    //  - 256-token x 256-row tiles (f16 only) when whole tiles go round every SM, the token tiles pair up without
+    //    padding (or the padding is under an eighth), and either K is long enough to pay for the larger epilogue
+    //    or there are four rounds of tiles;
+    //  - else 256-row tiles when there is a tile for every SM, or for 384 tokens and more with K up to 11008
+    //    (every tile is split over K then, but the wider tile re-reads the token block half as often);
+    //  - else 128-row tiles: every tile is split over K anyway and the narrower tile halves the partial results.
+    const int mt = (n + TM - 1) / TM;
+    const long long tiles256 = (long long)mt * ((M + 255) / 256);
     static const int force_tn = getenv("RLB_GEMM_TN") ? atoi(getenv("RLB_GEMM_TN")) : 0;  // experiments: 128, 256 or 512 (= 256-token tiles)
     if (!TF32) {
-        // 256-token tiles when there are enough of them to hand out whole tiles to every SM
         const long long tiles_big = (long long)((n + 2 * TM - 1) / (2 * TM)) * ((M + 255) / 256);
-        if (force_tn == 512 || (force_tn == 0 && n > TM && tiles_big >= ctx->sm_count))
+        const bool pairs = mt % 2 == 0 || mt >= 9;
+        const bool big = n > TM && pairs && tiles_big >= ctx->sm_count && (K >= 6144 || tiles_big >= 4LL * ctx->sm_count);
+        if (force_tn == 512 || (force_tn == 0 && big))
             return launch_tn<OT, false, 256, 2>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
     }
     if (force_tn == 256) return launch_tn<OT, TF32, 256, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
-    if (force_tn == 128 || tiles256 < ctx->sm_count) return launch_tn<OT, TF32, 128, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
+    const bool narrow = tiles256 < ctx->sm_count && !(!TF32 && n >= 3 * TM && K <= 11008);
+    if (force_tn == 128 || (force_tn == 0 && narrow)) return launch_tn<OT, TF32, 128, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
     return launch_tn<OT, TF32, 256, 1>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, round_out, err);
 }
 

@@ -96,7 +96,6 @@ struct rlb_model {
     void* pf_o = nullptr;
     float* pf_p = nullptr;
     float* pf_g1 = nullptr;
-    float* pf_g3 = nullptr;
     void* pf_g = nullptr;
     float* pf_last = nullptr;
 
@@ -382,7 +381,7 @@ int ensure_prefill_buffers(rlb_model* m, int n) {
     if (n <= m->pf_cap) return RLB_OK;
     cudaStreamSynchronize(m->ctx->stream);
     void** ptrs[] = {(void**)&m->pf_tokens, (void**)&m->pf_x, &m->pf_a, (void**)&m->pf_qkv, &m->pf_o, (void**)&m->pf_p,
-                     (void**)&m->pf_g1, (void**)&m->pf_g3, &m->pf_g, (void**)&m->pf_last};
+                     (void**)&m->pf_g1, &m->pf_g, (void**)&m->pf_last};
     for (void** p : ptrs) { if (*p) cudaFree(*p); *p = nullptr; }
     m->pf_cap = 0;
     const size_t N = (size_t)n, d = m->p.dim;
@@ -706,7 +705,7 @@ int rlb_model_free(rlb_model* m) {
     if (m->xbuf) cudaFree(m->xbuf);
     void* ptrs[] = {m->tok_emb, m->norm, m->output, m->rope, m->xa, m->xb, m->qbuf, m->obuf, m->gbuf, m->part_wo, m->part_w2,
                     m->logits_local, m->logits, m->scalars, m->tokens_out, m->attn_scratch, m->attn_counters, m->pf_tokens, m->pf_x,
-                    m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g3, m->pf_g, m->pf_last};
+                    m->pf_a, m->pf_qkv, m->pf_o, m->pf_p, m->pf_g1, m->pf_g, m->pf_last};
     for (void* p : ptrs) if (p) cudaFree(p);
     for (auto& W : m->L) {
         if (W.host) {  // the matrix pointers address the shared staging buffer

@@ -211,6 +211,23 @@ def test_prefill_equals_token_by_token_and_chunked(cuda_ctx):
     assert np.abs(k_full - k_chunk).max() <= 1e-5 * np.abs(k_full).max()
 
 
+def test_chunked_prefill_f16_on_tensor_cores(cuda_ctx):
+    """f16: a prompt given in two chunks (the second one at start_pos > 0 goes through the tensor-core attention
+    with its mask offset and through the tensor-core GEMM) agrees with the same prompt given at once and with the
+    oracle's logits for it."""
+    cfg = cfg_variant("tiny", dim=512, n_heads=4, n_layers=2, vocab=2000, max_seq_len=256)   # head_dim 128
+    gpu, orc = build_pair(cfg, True, cuda_ctx)
+    toks = S.synth_tokens(200, cfg["vocab"])
+    want = orc.forward(toks, 0, orc.make_caches())
+    full = gpu.forward(toks, 0, gpu.make_caches())
+    c = gpu.make_caches()
+    gpu.forward(toks[:70], 0, c)
+    chunked = gpu.forward(toks[70:], 70, c)
+    assert float(np.abs(full - want).max()) <= F16_ABS
+    assert float(np.abs(chunked - want).max()) <= F16_ABS
+    assert float(np.abs(chunked - full).max()) <= F16_ABS / 4
+
+
 def test_device_greedy_loop_equals_host_loop(cuda_ctx):
     cfg = cfg_variant("tiny", n_layers=3, vocab=4000)
     for f16 in (False, True):
