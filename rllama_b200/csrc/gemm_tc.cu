@@ -129,73 +129,12 @@ using gemm_sched::PieceIter;
 
 // a, b <- the f16 values nearest to them (ties to even), as f32. One packed conversion for the pair and two
 // mixed-precision adds of -0 (exact, sign of zero kept) instead of four conversions: the conversion unit issues a
-// sixteenth of what the FMA pipe does, and a tile's epilogue converts every element it stores.
+// fraction of what the FMA pipe does, and a tile's epilogue converts every element it stores.
 __device__ __forceinline__ void round_pair_f16(float& a, float& b) {
     const __half2 h = __floats2half2_rn(a, b);
     const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h);
     asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(a) : "h"((unsigned short)(hb & 0xffffu)), "f"(-0.0f));
     asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(b) : "h"((unsigned short)(hb >> 16)), "f"(-0.0f));
-}
-
-// 32 consecutive f32 columns of this thread's tensor-memory lane (two loads of 16; the caller waits for them).
-__device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
-#pragma unroll
-    for (int h = 0; h < 2; h++)
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-            : "=r"(r[16 * h + 0]), "=r"(r[16 * h + 1]), "=r"(r[16 * h + 2]), "=r"(r[16 * h + 3]), "=r"(r[16 * h + 4]), "=r"(r[16 * h + 5]),
-              "=r"(r[16 * h + 6]), "=r"(r[16 * h + 7]), "=r"(r[16 * h + 8]), "=r"(r[16 * h + 9]), "=r"(r[16 * h + 10]), "=r"(r[16 * h + 11]),
-              "=r"(r[16 * h + 12]), "=r"(r[16 * h + 13]), "=r"(r[16 * h + 14]), "=r"(r[16 * h + 15])
-            : "r"(taddr + 16 * h));
-}
-
-// One warp stores 32 tokens (row = lane) x 32 columns starting at column `col0` of the output: converted to OT
-// (f32 optionally rounded to the nearest f16 value), laid in the warp's staging rows of 32 * sizeof(OT) bytes with the
-// 16-byte chunks XOR-swizzled by row, then written out as whole rows. `C` is 16-byte aligned, ldc a multiple of 16 bytes.
-template <typename OT>
-__device__ __forceinline__ void store_unit(const uint32_t (&r)[32], unsigned char* stg, int lane, OT* __restrict__ C, int64_t ldc, int tok0,
-                                           int n, int col0, int Mrows, int round_out) {
-    constexpr int ROWB = 32 * (int)sizeof(OT);   // 128 (f32) or 64 (f16)
-    constexpr int CPR = ROWB / 16;               // chunks per row: 8 or 4
-    constexpr int EPC = 16 / (int)sizeof(OT);    // columns per chunk: 4 or 8
-    const int key = ROWB == 128 ? (lane & 7) : ((lane >> 1) & 3);
-#pragma unroll
-    for (int j = 0; j < CPR; j++) {
-        uint32_t w[4];
-        if (sizeof(OT) == 4) {
-#pragma unroll
-            for (int e = 0; e < 4; e += 2) {
-                float v0 = __uint_as_float(r[4 * j + e]), v1 = __uint_as_float(r[4 * j + e + 1]);
-                if (round_out) round_pair_f16(v0, v1);
-                w[e] = __float_as_uint(v0);
-                w[e + 1] = __float_as_uint(v1);
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const __half2 hh = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
-                w[e] = *reinterpret_cast<const uint32_t*>(&hh);
-            }
-        }
-        *reinterpret_cast<uint4*>(stg + lane * ROWB + ((j ^ key) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    __syncwarp();
-#pragma unroll
-    for (int it = 0; it < CPR; it++) {   // 32 / CPR rows per instruction, CPR lanes per row
-        const int rr = it * (32 / CPR) + lane / CPR, ch = lane % CPR;
-        const int rkey = ROWB == 128 ? (rr & 7) : ((rr >> 1) & 3);
-        const uint4 d = *reinterpret_cast<const uint4*>(stg + rr * ROWB + ((ch ^ rkey) * 16));
-        const int tok = tok0 + rr, col = col0 + ch * EPC;
-        if (tok < n && col < Mrows) {
-            OT* dst = C + (int64_t)tok * ldc + col;
-            if (col + EPC <= Mrows) *reinterpret_cast<uint4*>(dst) = d;
-            else {
-                const OT* e = reinterpret_cast<const OT*>(&d);
-                for (int x = 0; x < Mrows - col; x++) dst[x] = e[x];
-            }
-        }
-    }
-    __syncwarp();
 }
 
 template <typename OT> struct OutPack;
@@ -216,8 +155,10 @@ template <> struct OutPack<__half> {
         if (vec && valid_cols >= 16) {
             uint32_t w[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++)
-                w[j] = (uint32_t)__half_as_ushort(__float2half_rn(v[2 * j])) | ((uint32_t)__half_as_ushort(__float2half_rn(v[2 * j + 1])) << 16);
+            for (int j = 0; j < 8; j++) {
+                const __half2 hh = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
             reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
             reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
         } else {
@@ -263,10 +204,6 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
     const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x, TN, TT);
 
     if (threadIdx.x == 0) {
-        // (the descriptors' first use would otherwise wait for their fetch)
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_w)) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_x)) : "memory");
-        if (TF32) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tm_x2)) : "memory");
         dead_flag = 0;
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full_bar[s], 1);
@@ -383,32 +320,6 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
             const int token = mt * TT + half * TM + q * 32 + lane;
             const int col_base = nt * TN;
             float* slab = p.slot >= 0 ? part + ((size_t)blockIdx.x * 2 + p.slot) * kSlabFloats + (size_t)(half * TM + q * 32 + lane) * TN : nullptr;
-            if (!slab && vec_c) {
-                // Direct store of a finished tile, 16-byte aligned output, in units of 32 columns: the warp lays its
-                // 32 tokens x 32 converted columns in its own shared memory (row = token = lane; 16-byte chunks
-                // XOR-swizzled by row: no bank conflicts either way), then writes them out as whole rows of 128 bytes
-                // (f32; 64 bytes for f16), 4 (8) token rows per instruction. A thread storing its own token row
-                // touches 32 different lines per instruction. The tensor-memory loads of the next unit are in flight
-                // while a unit is converted and stored (two register buffers).
-                unsigned char* stg = tiles + kRingBytes + (size_t)(warp - 2) * 4096;
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (b + (uint32_t)half) * TN;
-                const int cols = Mrows - col_base < TN ? Mrows - col_base : TN;
-                const int nu = (cols + 31) / 32;   // (uniform over the warp)
-                const int tok0 = mt * TT + half * TM + q * 32;
-                uint32_t ra[32], rb[32];
-                tmem_ld32(ra, taddr);
-#pragma unroll 1
-                for (int u = 0; u < nu; u += 2) {
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (u + 1 < nu) tmem_ld32(rb, taddr + 32 * (u + 1));
-                    store_unit<OT>(ra, stg, lane, C, ldc, tok0, n, col_base + 32 * u, Mrows, round_out);
-                    if (u + 1 < nu) {
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (u + 2 < nu) tmem_ld32(ra, taddr + 32 * (u + 2));
-                        store_unit<OT>(rb, stg, lane, C, ldc, tok0, n, col_base + 32 * (u + 1), Mrows, round_out);
-                    }
-                }
-            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < TN; c0 += 32) {
                 if (col_base + c0 >= Mrows) break;  // (uniform over the warp)
@@ -435,7 +346,7 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
                     } else if (token < n && col_base + cc < Mrows) {
                         if (round_out) {
 #pragma unroll
-                            for (int j = 0; j < 16; j++) v[j] = __half2float(__float2half_rn(v[j]));
+                            for (int j = 0; j < 16; j += 2) round_pair_f16(v[j], v[j + 1]);
                         }
                         OutPack<OT>::store16(C + (int64_t)token * ldc + col_base + cc, v, vec_c, Mrows - (col_base + cc));
                     }
@@ -618,7 +529,7 @@ int launch_tn(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W, int64_t l
         RLB_TRY(make_map(&tx, X, n, K, ldx, TT));
         tx2 = tx;
     }
-    const size_t smem = (size_t)kRingBytes + 1024 + (size_t)4096 * 4 * MT;   // ring, alignment slack, 4 KB of staging per epilogue warp
+    const size_t smem = (size_t)kRingBytes + 1024;
     auto kern = gemm_tc_kernel<OT, TF32, TN, MT>;
     static std::atomic<uint64_t> set{0};
     if (!attr_done(set, ctx->device)) {
