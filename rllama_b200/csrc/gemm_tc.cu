@@ -377,7 +377,6 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     __shared__ int seg_slab[kMaxGrid];   // slab index (cta * 2 + slot) of CTA c's piece of this tile, or -1
     __shared__ int c_lo_s, c_hi_s;
     rlb_pdl_trigger();
-    rlb_pdl_wait();
     const Sched s = make_sched(n, Mrows, nkb, grid, TN, TT);
     const int j = blockIdx.x;
     if (threadIdx.x == 0) { c_lo_s = grid; c_hi_s = -1; }
@@ -393,6 +392,7 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     __syncthreads();
     const int c_lo = c_lo_s, c_hi = c_hi_s;
     if (c_lo >= c_hi) return;  // one CTA computed the whole tile and stored it itself
+    rlb_pdl_wait();            // (the schedule above needs nothing from the GEMM; its partial tiles do)
     const int tile = s.whole + j;
     const int nt = tile / s.n_mt, mt = tile - nt * s.n_mt;
     const int row0 = blockIdx.y * 8;
