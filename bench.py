@@ -94,6 +94,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        """The timed region starts here: samples before it (the warm-up steps, the same load) are used only when the
+        region is shorter than the sampling period and caught none."""
+        self.first = len(self.lines)
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -105,7 +110,9 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        timed = self.lines[getattr(self, "first", 0):]
+        window = "timed region" if timed else "prefill, warm-up and timed region (the timed region fell between two 100 ms samples)"
+        for ln in (timed or self.lines):
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -117,7 +124,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def torch_weights(cfg, device, seed=1234):
@@ -287,16 +294,17 @@ def measure(model, cfg, cl, D, local_rank, K, Wm, do_e2e=True):
     model.forward_greedy(prompt, 0, scratch)
     scratch.free()
     caches = model.make_caches()
+    sampler = ClockSampler(local_rank)   # (started early: nvidia-smi takes a while to deliver its first sample)
+    sampler.start()
     D.barrier(cl)
     t0 = time.perf_counter()
     first = model.forward_greedy(prompt, 0, caches)
     cl.flush()
     prefill_ms = D.max((time.perf_counter() - t0) * 1e3)
     warm_tokens, _ = model.decode_greedy(first, P, Wm, caches)
-    sampler = ClockSampler(local_rank)
     D.barrier(cl)
     launches0 = cl.kernel_launches()
-    sampler.start()
+    sampler.mark()
     tokens, dev_ms = model.decode_greedy(int(warm_tokens[-1]), P + Wm, K, caches)
     D.barrier(cl)
     clocks = sampler.stop()
@@ -385,6 +393,43 @@ def gemm_sweep():
             W.free(); X.free(); out.free()
 
 
+def gemm_trace():
+    """Per-CTA timeline of the prefill GEMM (needs the timeline build: ``python -m rllama_b200.build --trace`` and
+    ``RLLAMA_B200_LIB=rllama_b200/librllama_b200_trace.so``). One JSON line per shape: medians over the CTAs, us from
+    the first CTA's entry; `starved` / `acc_wait` = MMA thread blocked on operand stages / on a busy accumulator."""
+    import ctypes
+    from rllama_b200 import F16, Cuda, _ffi
+    L = _ffi.lib()
+    if not hasattr(L, "rlb_debug_gemm_trace"):
+        raise SystemExit("this library has no timeline: build it with `python -m rllama_b200.build --trace` and set "
+                         "RLLAMA_B200_LIB=rllama_b200/librllama_b200_trace.so")
+    L.rlb_debug_gemm_trace.argtypes = [ctypes.c_void_p]
+    cl = Cuda(verbose=False, nth_device=0)
+    rng = np.random.default_rng(0)
+    block = rng.normal(0, 0.02, size=(1024, 22016)).astype(np.float16)
+    for (M, K, n) in ((22016, 4096, 128), (4096, 4096, 128), (4096, 11008, 128), (12288, 4096, 128), (22016, 4096, 512),
+                      (12288, 4096, 1024), (22016, 4096, 2048), (44032, 8192, 1792)):
+        W = cl.upload(np.ascontiguousarray(np.tile(block[:, :K], ((M + 1023) // 1024, 1))[:M]))
+        X = cl.upload(rng.normal(0, 1.0, size=(n, K)).astype(np.float16))
+        out = cl.zeros(n, M, F16)
+        for _ in range(4):
+            out.matrix_mul_inplace_transposed(X, W)
+        cl.flush()
+        buf = np.zeros(256 * 16, dtype=np.uint64)
+        if L.rlb_debug_gemm_trace(buf.ctypes.data_as(ctypes.c_void_p)) != 0:
+            raise SystemExit("reading the trace failed")
+        t = buf.reshape(256, 16).astype(np.int64)
+        t = t[t[:, 0] > 0]
+        t0 = t[:, 0].min()
+        med = lambda v: round(float(np.median(v)) / 1e3, 2)
+        print(json.dumps({"M": M, "K": K, "tokens": n, "ctas": int(len(t)), "k_blocks_per_cta": int(np.median(t[:, 10])),
+                          "first_stage_us": med(t[:, 3] - t0), "starved_us": med(t[:, 5]), "acc_wait_us": med(t[:, 6]),
+                          "last_mma_us": [med(t[:, 4] - t0), round(float((t[:, 4] - t0).max()) / 1e3, 2)],
+                          "epilogue_end_us": [med(t[:, 8] - t0), round(float((t[:, 8] - t0).max()) / 1e3, 2)],
+                          "epilogue_busy_us": med(t[:, 13]), "ring_full_us": med(t[:, 11])}), flush=True)
+        W.free(); X.free(); out.free()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -401,7 +446,11 @@ def main():
     ap.add_argument("--f32", action="store_true", help="keep the weights and caches in f32 (the reference without --f16)")
     ap.add_argument("--gemm-sweep", action="store_true",
                     help="time the prefill GEMM (rlb_matrix_mul_inplace_transposed, f16) over prompt lengths and layer shapes, then exit")
+    ap.add_argument("--gemm-trace", action="store_true",
+                    help="per-CTA timeline of the prefill GEMM (timeline build of the library, see gemm_trace), then exit")
     args = ap.parse_args()
+    if args.gemm_trace:
+        return gemm_trace()
     if args.gemm_sweep:
         return gemm_sweep()
 

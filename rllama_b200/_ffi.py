@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librllama_b200.so")
+# RLLAMA_B200_LIB selects another build of the same library (the timeline build of ``rllama_b200.build --trace``)
+LIB_PATH = os.environ.get("RLLAMA_B200_LIB") or os.path.join(_HERE, "librllama_b200.so")
 
 F32, F16 = 0, 1
 

@@ -25,7 +25,12 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, trace=False):
+    """Builds the library (and the command-line program). ``trace=True`` builds a second library,
+    ``librllama_b200_trace.so``, whose prefill GEMM stamps a per-CTA timeline (``bench.py --gemm-trace`` reads it;
+    select it with ``RLLAMA_B200_LIB``); the product library is left alone."""
+    if trace:
+        return _build_trace(verbose)
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "rllama_b200.h"))
@@ -58,6 +63,25 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def _build_trace(verbose=False):
+    obj = os.path.join(OBJ, "trace")
+    os.makedirs(obj, exist_ok=True)
+    lib = os.path.join(HERE, "librllama_b200_trace.so")
+    objs = []
+    for src in SOURCES:
+        o = os.path.join(obj, src.replace(".cu", ".o"))
+        objs.append(o)
+        cmd = [NVCC] + FLAGS + ["-DRLB_GEMM_TRACE", "-c", os.path.join(CSRC, src), "-o", o]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout, r.stderr))
+    cmd = [NVCC, "-shared", "-o", lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl", "-lz"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed: %s\n%s" % (r.stdout, r.stderr))
+    return lib
+
+
 def build_cli(force=False):
     """The command-line program (host C++ over the C ABI): ``rllama_b200/bin/rllama-b200``."""
     src = os.path.join(HERE, "cli", "rllama_cli.cpp")
@@ -73,4 +97,4 @@ def build_cli(force=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -121,6 +121,26 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+#ifdef RLB_GEMM_TRACE
+// Timeline build (`python -m rllama_b200.build --trace`, a separate library): every CTA of the most recent GEMM launch
+// leaves 16 words in g_trace, times in ns of %globaltimer: 0 entry, 1 set-up done, 2 producer past its dependency
+// wait, 3 first operand stage landed, 4 last MMA committed, 5 MMA thread blocked on operand stages (total), 6 on a
+// busy accumulator (total), 7 first accumulator handed to the epilogue, 8 epilogue done, 9 epilogue blocked (total),
+// 10 k-blocks computed, 11 producer blocked on full ring (total), 12 producer done, 13 epilogue busy (total).
+// `bench.py --gemm-trace` reads them through rlb_debug_gemm_trace.
+__device__ unsigned long long g_trace[256 * 16];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define RLB_TR(i, v) (g_trace[blockIdx.x * 16 + (i)] = (unsigned long long)(v))
+#define RLB_NOW() trace_now()
+#else
+#define RLB_TR(i, v) ((void)0)
+#define RLB_NOW() 0ull
+#endif
+
 using gemm_sched::Sched;
 using gemm_sched::make_sched;
 using gemm_sched::rest_begin;
@@ -200,6 +220,7 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
     volatile int* dead = &dead_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) RLB_TR(0, RLB_NOW());
     const int nkb = (K + BKE - 1) / BKE;
     const Sched sched = make_sched(n, Mrows, nkb, (int)gridDim.x, TN, TT);
 
@@ -225,6 +246,7 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) RLB_TR(1, RLB_NOW());
     rlb_pdl_trigger();
     if (!(warp == 0 && lane == 0)) rlb_pdl_wait();  // (the producer thread waits after its weight prefetch)
 
@@ -250,6 +272,8 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
             advance();
         }
         rlb_pdl_wait();
+        RLB_TR(2, RLB_NOW());
+        unsigned long long tr_ring = 0;
         for (int i = 0; i < npre; i++) {
             unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
             tma_load_2d(st, &tm_x, pre_kb[i] * BKE, pre_mt[i] * TT, &full_bar[i]);   // (one box of TT rows)
@@ -259,7 +283,9 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
         while (have) {
             const int nt = p.tile / sched.n_mt, mt = p.tile - nt * sched.n_mt;
             const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
+            const unsigned long long tr_a = RLB_NOW();
             if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, err)) break;
+            tr_ring += RLB_NOW() - tr_a;
             unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
             tma_load_2d(st, &tm_x, kb * BKE, mt * TT, &full_bar[s]);
@@ -268,6 +294,8 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
             cnt++;
             advance();
         }
+        RLB_TR(11, tr_ring);
+        RLB_TR(12, RLB_NOW());
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
         // instruction descriptor: f32 accumulator, A and B both K-major, N = TN, M = TM
@@ -277,16 +305,23 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
         Piece p;
         uint32_t cnt = 0, piece = 0;
         bool ok = true;
+        unsigned long long tr_starved = 0, tr_acc = 0, tr_first = 0;
         while (ok && it.next(p)) {
             const uint32_t b = NACC == 2 ? (piece & 1u) : 0u;
             const uint32_t use = NACC == 2 ? (piece >> 1) : piece;  // how often this accumulator set has been used before
+            const unsigned long long tr_a = RLB_NOW();
             ok = mbar_wait(&acc_empty[b], (use & 1u) ^ 1u, dead, err);  // the epilogue has drained this accumulator
+            tr_acc += RLB_NOW() - tr_a;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t d = tmem_base + b * TN;
             for (int kb = p.kb0; kb < p.kb1; kb++, cnt++) {
                 const uint32_t s = cnt % kStages, ph = (cnt / kStages) & 1u;
+                const unsigned long long tr_b = RLB_NOW();
                 ok = mbar_wait(&full_bar[s], ph, dead, err);
+                const unsigned long long tr_c = RLB_NOW();
+                tr_starved += tr_c - tr_b;
+                if (!tr_first) tr_first = tr_c;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t x_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -303,16 +338,22 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
             if (ok) umma_commit(&acc_full[b]);
             piece++;
         }
+        RLB_TR(3, tr_first); RLB_TR(4, RLB_NOW()); RLB_TR(5, tr_starved); RLB_TR(6, tr_acc); RLB_TR(10, cnt);
     } else if (warp >= 2) {
         // ---------------- epilogue: four warps per 128-token block, one TMEM lane quarter (32 tokens) each ----------------
         const int q = warp & 3, half = (warp - 2) >> 2;
         PieceIter it(sched, (int)blockIdx.x, (int)gridDim.x);
         Piece p;
         uint32_t piece = 0;
+        unsigned long long tr_wait = 0, tr_busy = 0, tr_first = 0;
         const bool vec_c = ((ldc * (int64_t)sizeof(OT)) % 16 == 0) && (((uintptr_t)C & 15) == 0);
         while (it.next(p)) {
             const uint32_t b = NACC == 2 ? (piece & 1u) : 0u;
+            const unsigned long long tr_a = RLB_NOW();
             const bool ok = mbar_wait(&acc_full[b], (NACC == 2 ? (piece >> 1) : piece) & 1u, dead, err);
+            const unsigned long long tr_b = RLB_NOW();
+            tr_wait += tr_b - tr_a;
+            if (!tr_first) tr_first = tr_b;
             __syncwarp();
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -355,8 +396,10 @@ __global__ void __launch_bounds__(tc_threads(MT), 1) gemm_tc_kernel(const __grid
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
+            tr_busy += RLB_NOW() - tr_b;
             piece++;
         }
+        if (warp == 2 && lane == 0) { RLB_TR(7, tr_first); RLB_TR(8, RLB_NOW()); RLB_TR(9, tr_wait); RLB_TR(13, tr_busy); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -605,3 +648,10 @@ int launch_gemm_tc_f32w(rlb_ctx* ctx, const void* X, int64_t ldx, const void* W,
                         int* err) {
     return launch_tc<float, true>(ctx, X, ldx, W, ldw, C, ldc, n, M, K, 0, err);
 }
+
+#ifdef RLB_GEMM_TRACE
+// (timeline build only; not part of the ABI in include/rllama_b200.h) copies the 256 x 16 trace words to `out`
+extern "C" int rlb_debug_gemm_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 256 * 16);
+}
+#endif
