@@ -43,6 +43,7 @@
 #include <cstdlib>
 
 #include "gemm_sched.h"
+#include "round_f16.h"
 #include "internal.h"
 
 namespace {
@@ -146,16 +147,6 @@ using gemm_sched::make_sched;
 using gemm_sched::rest_begin;
 using gemm_sched::Piece;
 using gemm_sched::PieceIter;
-
-// a, b <- the f16 values nearest to them (ties to even), as f32. One packed conversion for the pair and two
-// mixed-precision adds of -0 (exact, sign of zero kept) instead of four conversions: the conversion unit issues a
-// fraction of what the FMA pipe does, and a tile's epilogue converts every element it stores.
-__device__ __forceinline__ void round_pair_f16(float& a, float& b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h);
-    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(a) : "h"((unsigned short)(hb & 0xffffu)), "f"(-0.0f));
-    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(b) : "h"((unsigned short)(hb >> 16)), "f"(-0.0f));
-}
 
 template <typename OT> struct OutPack;
 template <> struct OutPack<float> {

@@ -65,6 +65,24 @@ def test_matrix_mul_transposed_many_tiles(cuda_ctx, n, M, K):
     assert (got == want).mean() > 0.97  # same f32 sums up to order, one f16 rounding
 
 
+def test_gemm_epilogue_rounding_matches_plain_conversions(tmp_path):
+    """The prefill GEMM rounds its f32 accumulators to f16 values with a packed conversion and a mixed-precision
+    add (csrc/round_f16.h). tests/cuda/round_pair_check.cu compares that on the device, bit for bit, with
+    __float2half_rn / __half2float: every f16 bit pattern for the widening (subnormals, infinities, NaN), 2^26 f32
+    bit patterns and their negatives for the rounding."""
+    import os, shutil, subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc on this machine to build the check program")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "round_pair_check")
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-I", os.path.join(root, "rllama_b200", "csrc"),
+                    "-o", exe, os.path.join(root, "tests", "cuda", "round_pair_check.cu")], check=True, capture_output=True, text=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "widening mismatches: 0; rounding mismatches: 0" in r.stdout
+
+
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
 def test_matrix_mul_transposed_random_sizes(cuda_ctx, dtype):
     # src/tensor.rs:2986-3090: sizes up to 300, including one row on either side; 1e-2
