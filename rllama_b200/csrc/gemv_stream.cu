@@ -94,6 +94,9 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// (private to this file) PRO_NORM whose tensor-parallel consumer gathers the whole row in every CTA
+constexpr int PRO_NORM_GATHER = 2;
+
 // Tensor-parallel exchange entries: {f32 value, u32 sequence number} in one 8-byte store.
 __device__ __forceinline__ void ll_store(uint2* p, float v, uint32_t seq) {
     asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
@@ -124,6 +127,47 @@ __device__ __forceinline__ void ll_gather(const uint2* base, size_t stride, int 
     if (pend != 0) {
         *dead = 1;
         atomicExch(err, 2);
+    }
+}
+
+// The same poll for a whole row: the thread's G groups of four consecutive entries (element tid * 4 + g * 4 * stride4)
+// from `count` ranks, rank r's row at base + r * K; sum[g] = entries of rank 0 + rank 1 + ... in that order. A group is
+// two 16-byte loads (four {value, sequence} entries); all pending groups of a rank are requested before any is examined.
+template <int G>
+__device__ __forceinline__ void ll_gather_row(const uint2* base, int K, int count, uint32_t seq, int tid, int stride4, float4 (&sum)[G],
+                                              volatile int* dead, int* err) {
+    uint32_t valid = 0;
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        sum[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tid * 4 + g * 4 * stride4 < K) valid |= 1u << g;
+    }
+    for (int r = 0; r < count; r++) {
+        const uint2* row = base + (size_t)r * K;
+        uint32_t pend = valid;
+        for (uint32_t it = 0; pend != 0 && it < (1u << 20); it++) {
+            uint4 lo[G], hi[G];
+#pragma unroll
+            for (int g = 0; g < G; g++)
+                if (pend & (1u << g)) {
+                    const uint2* p = row + tid * 4 + g * 4 * stride4;
+                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(lo[g].x), "=r"(lo[g].y), "=r"(lo[g].z), "=r"(lo[g].w) : "l"(p) : "memory");
+                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(hi[g].x), "=r"(hi[g].y), "=r"(hi[g].z), "=r"(hi[g].w) : "l"(p + 2) : "memory");
+                }
+#pragma unroll
+            for (int g = 0; g < G; g++)
+                if ((pend & (1u << g)) && lo[g].y == seq && lo[g].w == seq && hi[g].y == seq && hi[g].w == seq) {
+                    sum[g].x += __uint_as_float(lo[g].x); sum[g].y += __uint_as_float(lo[g].z);
+                    sum[g].z += __uint_as_float(hi[g].x); sum[g].w += __uint_as_float(hi[g].z);
+                    pend &= ~(1u << g);
+                }
+            if ((it & 255u) == 255u && *dead) return;
+        }
+        if (pend != 0) {
+            *dead = 1;
+            atomicExch(err, 2);
+            return;
+        }
     }
 }
 
@@ -260,7 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
     constexpr int kRowGroups = G;
     constexpr bool kGainEarly = G <= 4;  // with 8 groups the registers are needed for the row itself
     float4 gain_r[kRowGroups];
-    if (PRO == PRO_NORM && kGainEarly && warp < kConsumerWarps) {
+    if (PRO != PRO_COPY && kGainEarly && warp < kConsumerWarps) {
 #pragma unroll
         for (int g = 0; g < kRowGroups; g++) {
             const int i = tid * 4 + g * 4 * kConsumers;
@@ -355,7 +399,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_stream_kernel(const GemvArgs
         if (a.tok_ptr) xin += (int64_t)(*a.tok_ptr) * K;
         float ss = 0.f;
         float4 xr[kRowGroups];  // this thread's elements of the residual row
-        if (a.ll_inbox != nullptr) {
+        if (PRO == PRO_NORM_GATHER && kRowGroups <= 4) {
+            // Tensor-parallel push exchange, short rows: every CTA collects the whole row's partial sums from every
+            // rank's entries itself (rank order, f16 rounding after the sum) and adds the residual; CTA 0 stores the new
+            // residual row for the kernels that follow. No CTA waits for another one.
+            constexpr int GG = kRowGroups <= 4 ? kRowGroups : 1;
+            const uint32_t seq = (uint32_t)(*a.epoch_ptr - 1) * a.seq_stride + a.seq_idx;
+#pragma unroll
+            for (int g = 0; g < GG; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                xr[g] = i < K ? ld_f4(xin + i) : make_float4(0.f, 0.f, 0.f, 0.f);  // requested before the poll
+            }
+            float4 sum[GG];
+            ll_gather_row<GG>(a.ll_inbox, K, a.n_parts, seq, tid, kConsumers, sum, dead, cfg.err);
+#pragma unroll
+            for (int g = 0; g < GG; g++) {
+                const int i = tid * 4 + g * 4 * kConsumers;
+                if (i < K) {
+                    float4 sacc = sum[g];
+                    if (a.round_parts) {
+                        sacc.x = round_f16(sacc.x); sacc.y = round_f16(sacc.y); sacc.z = round_f16(sacc.z); sacc.w = round_f16(sacc.w);
+                    }
+                    float4 v = xr[g];
+                    v.x += sacc.x; v.y += sacc.y; v.z += sacc.z; v.w += sacc.w;
+                    xr[g] = v;
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                    if (blockIdx.x == 0) *reinterpret_cast<float4*>(a.x_out + i) = v;
+                }
+            }
+        } else if (a.ll_inbox != nullptr) {
             // Tensor-parallel push exchange. This CTA owns a slice of the residual row: it collects
             // that slice's partial sums from every rank's entries (rank order, f16 rounding after the
             // sum), adds the residual and publishes the result as {value, sequence} entries; then
@@ -595,16 +667,16 @@ int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
     const ShapeCfg sc = pick_cfg(EPI, a);
     if (sc.rb == 0) return RLB_ERR_STATE;  // caller falls back to the register-staged kernel
     // (the two-vectors-per-lane variants J = 2 were measured slower at every shape and are not built)
-    const bool wide = PRO == PRO_NORM && a.K > 4096;
+    const bool wide = PRO != PRO_COPY && a.K > 4096;
     switch (sc.rb) {
         case 8:
-            return wide ? launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+            return wide ? launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI, (PRO != PRO_COPY ? 8 : 4)>(ctx, a, err_flag, pdl)
                         : launch_cfg<WT, (NMAT == 1 ? 8 : 4), 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
         case 4:
-            return wide ? launch_cfg<WT, 4, 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+            return wide ? launch_cfg<WT, 4, 1, PRO, EPI, (PRO != PRO_COPY ? 8 : 4)>(ctx, a, err_flag, pdl)
                         : launch_cfg<WT, 4, 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
         case 2:
-            return wide ? launch_cfg<WT, 2, 1, PRO, EPI, (PRO == PRO_NORM ? 8 : 4)>(ctx, a, err_flag, pdl)
+            return wide ? launch_cfg<WT, 2, 1, PRO, EPI, (PRO != PRO_COPY ? 8 : 4)>(ctx, a, err_flag, pdl)
                         : launch_cfg<WT, 2, 1, PRO, EPI, 4>(ctx, a, err_flag, pdl);
         default: break;
     }
@@ -613,6 +685,13 @@ int launch_shape(rlb_ctx* ctx, const GemvArgs& a, int* err_flag, bool pdl) {
 
 template <typename WT>
 int launch_typed(rlb_ctx* ctx, int prologue, int epilogue, const GemvArgs& a, int* err_flag, bool pdl) {
+    // the tensor-parallel consumer that gathers the whole row in every CTA is a kernel of its own, so that the
+    // single-GPU kernels carry none of its code (measured: 1.3 % on the 7B token when it was a run-time branch)
+    if (prologue == PRO_NORM && a.ll_inbox != nullptr && a.gather_all && a.K <= 4096) {
+        if (epilogue == EPI_QKV) return launch_shape<WT, PRO_NORM_GATHER, EPI_QKV>(ctx, a, err_flag, pdl);
+        if (epilogue == EPI_SWIGLU) return launch_shape<WT, PRO_NORM_GATHER, EPI_SWIGLU>(ctx, a, err_flag, pdl);
+        if (epilogue == EPI_F32) return launch_shape<WT, PRO_NORM_GATHER, EPI_F32>(ctx, a, err_flag, pdl);
+    }
     if (prologue == PRO_NORM && epilogue == EPI_QKV) return launch_shape<WT, PRO_NORM, EPI_QKV>(ctx, a, err_flag, pdl);
     if (prologue == PRO_NORM && epilogue == EPI_SWIGLU) return launch_shape<WT, PRO_NORM, EPI_SWIGLU>(ctx, a, err_flag, pdl);
     if (prologue == PRO_NORM && epilogue == EPI_F32) return launch_shape<WT, PRO_NORM, EPI_F32>(ctx, a, err_flag, pdl);

@@ -120,6 +120,7 @@ struct GemvArgs {
     int64_t out_offset = 0;
     const uint2* ll_inbox = nullptr; // PRO_NORM consumer: this rank's inbox, n_parts x K entries
     unsigned int* xready = nullptr;  // PRO_NORM consumer: counts the CTAs that have published their slice of x_out
+    int gather_all = 0;              // PRO_NORM consumer: every CTA collects the whole row from the inbox itself (short rows, few ranks)
     uint32_t seq_idx = 0, seq_stride = 0, out_seq_idx = 0;
     const int32_t* epoch_ptr = nullptr;
     // EPI_QKV
