@@ -237,7 +237,8 @@ int enqueue_decode_step(rlb_model* m, rlb_caches* c, bool advance) {
         // Short rows on few ranks: every CTA polls the whole row's entries itself (tp * dim * 8 bytes through L2 per
         // CTA) and the slice publication with its fence, counter and second L2 round trip falls away.
         static const int gather_kb = getenv("RLB_TP_GATHER_KB") ? atoi(getenv("RLB_TP_GATHER_KB")) : 64;
-        a.gather_all = d <= 4096 && (size_t)m->tp * (size_t)d * 8 <= (size_t)gather_kb * 1024;
+        // (two ranks only: the case that was measured and is covered by the 2-GPU tests)
+        a.gather_all = m->tp == 2 && d <= 4096 && (size_t)m->tp * (size_t)d * 8 <= (size_t)gather_kb * 1024;
     };
 
     for (int l = 0; l < m->p.n_layers; l++) {
