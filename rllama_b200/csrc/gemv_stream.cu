@@ -133,6 +133,8 @@ __device__ __forceinline__ void ll_gather(const uint2* base, size_t stride, int 
 // The same poll for a whole row: the thread's G groups of four consecutive entries (element tid * 4 + g * 4 * stride4)
 // from `count` ranks, rank r's row at base + r * K; sum[g] = entries of rank 0 + rank 1 + ... in that order. A group is
 // two 16-byte loads (four {value, sequence} entries); all pending groups of a rank are requested before any is examined.
+// (Every entry was written by one aligned 8-byte store and is read inside one aligned 16-byte access, so a value is never
+// seen with another store's sequence number; an entry of the pair that has not arrived yet just fails the comparison.)
 template <int G>
 __device__ __forceinline__ void ll_gather_row(const uint2* base, int K, int count, uint32_t seq, int tid, int stride4, float4 (&sum)[G],
                                               volatile int* dead, int* err) {
